@@ -1,0 +1,207 @@
+// Device-side prelude prepended to every generated recurrent kernel.
+//
+// The generated kernels are compiled at run time (NVRTC, sm_100a) without any
+// include path, so everything they need is defined here: 16-bit float
+// conversions, the 1-D TMA bulk copy (cp.async.bulk) with its mbarrier, a
+// time-bounded mbarrier wait that reports through an error word instead of
+// spinning for ever, and the warp-shuffle row reduction.
+//
+// When FRNN_EMU is defined the same source is compiled by a host C++ compiler
+// against a thread-per-CUDA-thread emulation (tests only); the PTX bodies are
+// then replaced by the emulation's definitions of the same functions.
+#pragma once
+
+#ifndef FRNN_EMU
+typedef unsigned short u16;
+typedef unsigned int u32;
+typedef unsigned long long u64;
+#define FRNN_DEV __device__ __forceinline__
+#define FRNN_DYN_SMEM(name) extern __shared__ __align__(128) unsigned char name[]
+
+FRNN_DEV float frnn_bf16_to_f32(u16 v) { return __uint_as_float(((u32)v) << 16); }
+FRNN_DEV u16 frnn_f32_to_bf16(float f) {
+    u16 r;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+    return r;
+}
+FRNN_DEV float frnn_f16_to_f32(u16 v) {
+    float r;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(r) : "h"(v));
+    return r;
+}
+FRNN_DEV u16 frnn_f32_to_f16(float f) {
+    u16 r;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(f));
+    return r;
+}
+
+FRNN_DEV u32 frnn_smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+
+FRNN_DEV u64 frnn_now_ns() {
+    u64 t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---- mbarrier + TMA bulk copy (global -> shared, no multicast) ------------
+FRNN_DEV void frnn_mbar_init(u64* bar, u32 count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(frnn_smem_addr(bar)), "r"(count) : "memory");
+}
+FRNN_DEV void frnn_mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+FRNN_DEV void frnn_async_proxy_fence() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+FRNN_DEV void frnn_mbar_expect_tx(u64* bar, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(frnn_smem_addr(bar)), "r"(bytes) : "memory");
+}
+// one 1-D bulk copy; dst, src 16-byte aligned, bytes a multiple of 16
+FRNN_DEV void frnn_bulk_g2s(void* dst_smem, const void* src_gmem, u32 bytes, u64* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            frnn_smem_addr(dst_smem)),
+        "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(frnn_smem_addr(bar))
+        : "memory");
+}
+FRNN_DEV bool frnn_mbar_try(u64* bar, u32 parity) {
+    u32 ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(frnn_smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+FRNN_DEV float frnn_shfl_xor(float v, int off) { return __shfl_xor_sync(0xffffffffu, v, off); }
+FRNN_DEV void frnn_block_sync() { __syncthreads(); }
+FRNN_DEV void frnn_warp_sync() { __syncwarp(); }
+FRNN_DEV void frnn_atomic_add(float* p, float v) { atomicAdd(p, v); }
+FRNN_DEV void frnn_report(int* err, int code) { atomicCAS(err, 0, code); }
+FRNN_DEV float frnn_expf(float x) { return __expf(x); }
+FRNN_DEV float frnn_logf(float x) { return __logf(x); }
+FRNN_DEV float frnn_sqrtf(float x) { return __fsqrt_rn(x); }
+FRNN_DEV float frnn_rcpf(float x) { return __frcp_rn(x); }
+FRNN_DEV float frnn_divf(float a, float b) { return __fdividef(a, b); }
+#endif  // !FRNN_EMU
+
+#ifndef FRNN_WAIT_LIMIT_NS
+#define FRNN_WAIT_LIMIT_NS 2000000000ull
+#endif
+
+// Bounded wait for a TMA stage.  Returns false (after recording `code` in the
+// error word) when the barrier has not completed within the time limit; the
+// caller then leaves the kernel, so a lost copy never becomes a hung GPU.
+FRNN_DEV bool frnn_mbar_wait(u64* bar, u32 parity, int* err, int code) {
+    if (frnn_mbar_try(bar, parity)) return true;
+    u64 t0 = frnn_now_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (frnn_mbar_try(bar, parity)) return true;
+        if (frnn_now_ns() - t0 > FRNN_WAIT_LIMIT_NS) {
+            frnn_report(err, code);
+            return false;
+        }
+    }
+}
+
+template <int DT> struct frnn_io;  // 0 = fp32, 1 = bf16, 2 = fp16, 3 = fp64
+template <> struct frnn_io<0> {
+    typedef float T;
+    static FRNN_DEV float ld(const void* p, long i) { return ((const float*)p)[i]; }
+    static FRNN_DEV void st(void* p, long i, float v) { ((float*)p)[i] = v; }
+};
+template <> struct frnn_io<1> {
+    typedef u16 T;
+    static FRNN_DEV float ld(const void* p, long i) { return frnn_bf16_to_f32(((const u16*)p)[i]); }
+    static FRNN_DEV void st(void* p, long i, float v) { ((u16*)p)[i] = frnn_f32_to_bf16(v); }
+};
+template <> struct frnn_io<2> {
+    typedef u16 T;
+    static FRNN_DEV float ld(const void* p, long i) { return frnn_f16_to_f32(((const u16*)p)[i]); }
+    static FRNN_DEV void st(void* p, long i, float v) { ((u16*)p)[i] = frnn_f32_to_f16(v); }
+};
+template <> struct frnn_io<3> {
+    typedef double T;
+    static FRNN_DEV float ld(const void* p, long i) { return (float)((const double*)p)[i]; }
+    static FRNN_DEV void st(void* p, long i, float v) { ((double*)p)[i] = (double)v; }
+};
+
+// sum over the L lanes (L a power of two <= 32) that share one state row
+template <int L> FRNN_DEV float frnn_row_sum(float v) {
+#pragma unroll
+    for (int off = L / 2; off > 0; off >>= 1) v += frnn_shfl_xor(v, off);
+    return v;
+}
+
+// ---- vector loads / stores with dtype conversion ---------------------------
+// frnn_ldv<DT,CNT>(base, i, out): out[0..CNT) = float(base[i .. i+CNT)), where
+// the CNT elements are fetched with the widest access their size allows.  The
+// caller guarantees that element i sits on a CNT-element boundary of a
+// 16-byte aligned base.  Works on shared and global memory alike.
+struct __align__(8) frnn_u2 { u32 x, y; };
+struct __align__(16) frnn_u4 { u32 x, y, z, w; };
+struct __align__(8) frnn_f2 { float x, y; };
+struct __align__(16) frnn_f4 { float x, y, z, w; };
+
+template <int DT> FRNN_DEV float frnn_lo16(u32 w);
+template <int DT> FRNN_DEV float frnn_hi16(u32 w);
+template <> FRNN_DEV float frnn_lo16<1>(u32 w) { return frnn_bf16_to_f32((u16)(w & 0xffffu)); }
+template <> FRNN_DEV float frnn_hi16<1>(u32 w) { return frnn_bf16_to_f32((u16)(w >> 16)); }
+template <> FRNN_DEV float frnn_lo16<2>(u32 w) { return frnn_f16_to_f32((u16)(w & 0xffffu)); }
+template <> FRNN_DEV float frnn_hi16<2>(u32 w) { return frnn_f16_to_f32((u16)(w >> 16)); }
+template <int DT> FRNN_DEV u32 frnn_pack16(float a, float b);
+template <> FRNN_DEV u32 frnn_pack16<1>(float a, float b) { return (u32)frnn_f32_to_bf16(a) | ((u32)frnn_f32_to_bf16(b) << 16); }
+template <> FRNN_DEV u32 frnn_pack16<2>(float a, float b) { return (u32)frnn_f32_to_f16(a) | ((u32)frnn_f32_to_f16(b) << 16); }
+
+template <int DT, int CNT> FRNN_DEV void frnn_ldv(const void* base, long i, float* out) {
+    if constexpr (DT == 0 && CNT == 4) {
+        frnn_f4 t = *(const frnn_f4*)((const float*)base + i);
+        out[0] = t.x; out[1] = t.y; out[2] = t.z; out[3] = t.w;
+    } else if constexpr (DT == 0 && CNT == 2) {
+        frnn_f2 t = *(const frnn_f2*)((const float*)base + i);
+        out[0] = t.x; out[1] = t.y;
+    } else if constexpr ((DT == 1 || DT == 2) && CNT == 8) {
+        frnn_u4 t = *(const frnn_u4*)((const u16*)base + i);
+        out[0] = frnn_lo16<DT>(t.x); out[1] = frnn_hi16<DT>(t.x);
+        out[2] = frnn_lo16<DT>(t.y); out[3] = frnn_hi16<DT>(t.y);
+        out[4] = frnn_lo16<DT>(t.z); out[5] = frnn_hi16<DT>(t.z);
+        out[6] = frnn_lo16<DT>(t.w); out[7] = frnn_hi16<DT>(t.w);
+    } else if constexpr ((DT == 1 || DT == 2) && CNT == 4) {
+        frnn_u2 t = *(const frnn_u2*)((const u16*)base + i);
+        out[0] = frnn_lo16<DT>(t.x); out[1] = frnn_hi16<DT>(t.x);
+        out[2] = frnn_lo16<DT>(t.y); out[3] = frnn_hi16<DT>(t.y);
+    } else if constexpr ((DT == 1 || DT == 2) && CNT == 2) {
+        u32 t = *(const u32*)((const u16*)base + i);
+        out[0] = frnn_lo16<DT>(t); out[1] = frnn_hi16<DT>(t);
+    } else {
+#pragma unroll
+        for (int k = 0; k < CNT; k++) out[k] = frnn_io<DT>::ld(base, i + k);
+    }
+}
+
+template <int DT, int CNT> FRNN_DEV void frnn_stv(void* base, long i, const float* v) {
+    if constexpr (DT == 0 && CNT == 4) {
+        frnn_f4 t; t.x = v[0]; t.y = v[1]; t.z = v[2]; t.w = v[3];
+        *(frnn_f4*)((float*)base + i) = t;
+    } else if constexpr (DT == 0 && CNT == 2) {
+        frnn_f2 t; t.x = v[0]; t.y = v[1];
+        *(frnn_f2*)((float*)base + i) = t;
+    } else if constexpr ((DT == 1 || DT == 2) && CNT == 8) {
+        frnn_u4 t;
+        t.x = frnn_pack16<DT>(v[0], v[1]); t.y = frnn_pack16<DT>(v[2], v[3]);
+        t.z = frnn_pack16<DT>(v[4], v[5]); t.w = frnn_pack16<DT>(v[6], v[7]);
+        *(frnn_u4*)((u16*)base + i) = t;
+    } else if constexpr ((DT == 1 || DT == 2) && CNT == 4) {
+        frnn_u2 t;
+        t.x = frnn_pack16<DT>(v[0], v[1]); t.y = frnn_pack16<DT>(v[2], v[3]);
+        *(frnn_u2*)((u16*)base + i) = t;
+    } else if constexpr ((DT == 1 || DT == 2) && CNT == 2) {
+        *(u32*)((u16*)base + i) = frnn_pack16<DT>(v[0], v[1]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < CNT; k++) frnn_io<DT>::st(base, i + k, v[k]);
+    }
+}

@@ -1,0 +1,145 @@
+"""ctypes binding of libfrnn_b200.so (see include/frnn.h) and a compile cache.
+
+The PyTorch custom op built in ``twopass.py`` reaches the GPU only through
+this module: NVRTC compilation of the generated source, module load on the
+tensors' device, and launches on ``torch.cuda.current_stream()``.  There is no
+other execution path: if the library is missing or the driver cannot be
+reached the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import threading
+from typing import Dict, List, Optional, Sequence, Tuple
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libfrnn_b200.so")
+
+SYMBOLS = ["frnn_abi_version", "frnn_last_error", "frnn_compile", "frnn_free", "frnn_module_load",
+           "frnn_module_unload", "frnn_launch", "frnn_kernel_attrs", "frnn_l2_flush", "frnn_fp32_peak_probe"]
+
+
+class FrnnError(RuntimeError):
+    pass
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib() -> ctypes.CDLL:
+    """Load the C-ABI library (building it first if the .so is absent)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            from . import build as _build
+            _build.build()
+        L = ctypes.CDLL(LIB_PATH)
+        vp, cp, sz, ci, cu = ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_uint
+        L.frnn_abi_version.restype = ci
+        L.frnn_last_error.restype = cp
+        L.frnn_compile.argtypes = [cp, ctypes.POINTER(cp), ci, ctypes.POINTER(vp), ctypes.POINTER(sz), cp, sz]
+        L.frnn_free.argtypes = [vp]
+        L.frnn_free.restype = None
+        L.frnn_module_load.argtypes = [vp, sz, ctypes.POINTER(cp), ctypes.POINTER(cu), ci, ctypes.POINTER(vp)]
+        L.frnn_module_unload.argtypes = [vp]
+        L.frnn_launch.argtypes = [vp, ci, ctypes.POINTER(cu), ctypes.POINTER(cu), cu, vp, ctypes.POINTER(vp), ci]
+        L.frnn_kernel_attrs.argtypes = [vp, ci, ctypes.POINTER(ci), ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        L.frnn_l2_flush.argtypes = [vp, sz, vp]
+        L.frnn_fp32_peak_probe.argtypes = [vp, ci, vp, ctypes.POINTER(ctypes.c_double)]
+        _lib = L
+    return _lib
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise FrnnError(f"{what} failed (code {rc}): {lib().frnn_last_error().decode(errors='replace')}")
+
+
+_cubin_cache: Dict[str, Tuple[bytes, str]] = {}
+
+
+def compile_cubin(src: str, opts: Sequence[str] = ()) -> Tuple[bytes, str]:
+    """NVRTC-compile ``src`` for sm_100a.  Returns (cubin, compiler log).
+    Needs no GPU.  Results are cached by source hash in memory and, when
+    ``FRNN_CACHE_DIR`` is set, on disk."""
+    key = hashlib.sha256((src + "\0" + "\0".join(opts)).encode()).hexdigest()
+    if key in _cubin_cache:
+        return _cubin_cache[key]
+    cdir = os.environ.get("FRNN_CACHE_DIR")
+    if cdir:
+        fn = os.path.join(cdir, key + ".cubin")
+        if os.path.exists(fn):
+            with open(fn, "rb") as f:
+                out = (f.read(), "(cached)")
+            _cubin_cache[key] = out
+            return out
+    L = lib()
+    arr = (ctypes.c_char_p * max(1, len(opts)))(*[o.encode() for o in opts])
+    cub = ctypes.c_void_p()
+    size = ctypes.c_size_t()
+    log = ctypes.create_string_buffer(1 << 16)
+    rc = L.frnn_compile(src.encode(), arr, len(opts), ctypes.byref(cub), ctypes.byref(size), log, len(log))
+    logtxt = log.value.decode(errors="replace")
+    if rc != 0:
+        raise FrnnError(f"frnn_compile failed (code {rc}): {L.frnn_last_error().decode(errors='replace')}\n{logtxt}")
+    data = ctypes.string_at(cub.value, size.value)
+    L.frnn_free(cub)
+    if cdir:
+        os.makedirs(cdir, exist_ok=True)
+        with open(os.path.join(cdir, key + ".cubin"), "wb") as f:
+            f.write(data)
+    _cubin_cache[key] = (data, logtxt)
+    return data, logtxt
+
+
+class Module:
+    """A loaded cubin with its kernels, bound to the device current at load."""
+
+    def __init__(self, cubin: bytes, names: Sequence[str], smem: Sequence[int]):
+        L = lib()
+        self._names = list(names)
+        n = len(names)
+        arr = (ctypes.c_char_p * n)(*[s.encode() for s in names])
+        sm = (ctypes.c_uint * n)(*[int(s) for s in smem])
+        h = ctypes.c_void_p()
+        self._buf = ctypes.create_string_buffer(cubin, len(cubin))
+        _check(L.frnn_module_load(self._buf, len(cubin), arr, sm, n, ctypes.byref(h)), "frnn_module_load")
+        self._h = h
+
+    def launch(self, kernel: int, grid: Sequence[int], block: int, smem: int, stream: int, ptrs: Sequence[int]):
+        """Launch with device pointers ``ptrs`` (ints) as the kernel parameters."""
+        n = len(ptrs)
+        vals = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(p)) for p in ptrs])
+        args = (ctypes.c_void_p * n)(*[ctypes.addressof(vals) + i * ctypes.sizeof(ctypes.c_void_p) for i in range(n)])
+        g = (ctypes.c_uint * 3)(*[int(x) for x in grid])
+        b = (ctypes.c_uint * 3)(int(block), 1, 1)
+        _check(lib().frnn_launch(self._h, kernel, g, b, int(smem), ctypes.c_void_p(int(stream)), args, n),
+               f"frnn_launch({self._names[kernel]})")
+
+    def attrs(self, kernel: int) -> Dict[str, int]:
+        r, s, l = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        _check(lib().frnn_kernel_attrs(self._h, kernel, ctypes.byref(r), ctypes.byref(s), ctypes.byref(l)), "frnn_kernel_attrs")
+        return {"regs": r.value, "static_smem": s.value, "local_bytes": l.value}
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().frnn_module_unload(self._h)
+            self._h = None
+
+
+def l2_flush(buf_ptr: int, nbytes: int, stream: int):
+    _check(lib().frnn_l2_flush(ctypes.c_void_p(buf_ptr), nbytes, ctypes.c_void_p(stream)), "frnn_l2_flush")
+
+
+def fp32_peak_probe(sink_ptr: int, iters: int, stream: int) -> float:
+    fl = ctypes.c_double()
+    _check(lib().frnn_fp32_peak_probe(ctypes.c_void_p(sink_ptr), iters, ctypes.c_void_p(stream), ctypes.byref(fl)),
+           "frnn_fp32_peak_probe")
+    return fl.value

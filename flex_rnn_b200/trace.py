@@ -1,0 +1,64 @@
+"""Tracing of a step function into a joint forward + backward graph.
+
+The reference obtains the joint graph with ``functorch.compile.aot_function``
+and, when a fake-tensor mode is active (that is, under ``torch.compile``),
+re-runs the trace in a child process (flex_rnn/trace_isolated.py:3-39 in the
+reference project).  Here the joint function ``(x, dy) -> (y, vjp(dy))`` is
+traced in-process with ``make_fx`` on meta tensors; an active fake / dispatch
+mode is suspended for the duration of the trace, so no child process is needed.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Sequence, Tuple
+
+import torch
+from torch.fx.experimental.proxy_tensor import make_fx
+from torch.utils._python_dispatch import _disable_current_modes
+
+from .graph import StepGraph, from_fx
+
+#: stand-in sizes used while tracing; distinct and > 1 so that a traced
+#: value's shape tells whether it varies over rows and/or columns
+TRACE_M, TRACE_N = 3, 5
+
+
+def as_tuple(x):
+    return tuple(x) if isinstance(x, (tuple, list)) else (x,)
+
+
+def trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: int,
+                has_m: bool = True, has_n: bool = True) -> Tuple[StepGraph, int, int]:
+    """Trace ``step`` on per-head tiles.
+
+    ``classes[i]`` is ``(over_m, over_n)`` of argument ``i`` (inputs first, then
+    states).  Returns the joint graph whose inputs are
+    ``[*step args, *d_outputs, *d_new_states]`` and whose outputs are
+    ``[*outputs, *new_states, *d_args]``, together with the number of outputs
+    and of states.
+    """
+    tm = TRACE_M if has_m else 1
+    tn = TRACE_N if has_n else 1
+    with _disable_current_modes():
+        args = tuple(torch.empty(tm if c[0] else 1, tn if c[1] else 1, device="meta") for c in classes)
+        counts: List[int] = []
+
+        def flat(*a):
+            y, s = step(*a)
+            y, s = as_tuple(y), as_tuple(s)
+            if not counts:
+                counts.extend([len(y), len(s)])
+            return tuple(t.float() for t in y) + tuple(t.float() for t in s)
+
+        outs = flat(*args)
+        n = len(args)
+
+        def joint(*a):
+            x, dy = a[:n], a[n:]
+            y, pull = torch.func.vjp(flat, *x)
+            return tuple(y) + tuple(pull(tuple(dy)))
+
+        gm = make_fx(joint)(*args, *[torch.empty_like(o) for o in outs])
+    g = from_fx(gm, "joint", (tm, tn))
+    assert len(g.inputs) == n + len(outs)
+    assert len(g.outputs) == len(outs) + n
+    return g, counts[0], counts[1]

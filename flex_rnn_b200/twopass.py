@@ -1,0 +1,387 @@
+"""Planner and host closures of the B200 backend.
+
+Same contract as the reference's ``flex_rnn.twopass`` (flex_rnn/twopass.py:44,
+191-192, 224-237, 343-366 in the reference project), which is what the ``jit``
+front end calls:
+
+    build_twopass(step, inputs, state, dryrun=False)
+        -> (forward, backward, forward_meta, backward_meta)   or, with dryrun,
+        -> (forward_meta, backward_meta)
+
+    forward(inputs, state0)  -> (*outputs[B,T,H,M], *final_states, *state_store, aux)
+    backward(doutput, dstateT, inputs, state_store, aux) -> (tuple(dinputs), tuple(dstate0))
+
+What differs is everything underneath: the joint graph is sliced into three
+sub-graphs (forward step, reduction-free re-step, backward step) instead of
+five, two kernels are generated instead of three (``lower.py``), they are
+compiled with NVRTC and launched through the C-ABI library on the current
+stream, checkpoints are stored untransposed every ``seg * nslots`` steps, and
+no dstate checkpoints or ``daux`` buffers exist.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch as th
+
+from . import lower
+from .graph import MN, M1, N1, S11, StepGraph
+from .lower import (DT_BF16, DT_F16, DT_F32, DT_F64, GradOut, Problem, TensorSpec, choose_tile,
+                    emit_backward, emit_forward)
+from .trace import as_tuple, trace_joint
+
+_DT = {th.float32: DT_F32, th.bfloat16: DT_BF16, th.float16: DT_F16, th.float64: DT_F64}
+_IO_DTYPES = (th.float32, th.bfloat16, th.float16, th.float64)
+_PRELUDE: Optional[str] = None
+
+
+def prelude() -> str:
+    global _PRELUDE
+    if _PRELUDE is None:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "frnn_device.cuh")) as f:
+            _PRELUDE = f.read()
+    return _PRELUDE
+
+
+# -- small helpers with the reference's names (flex_rnn/twopass.py:8-42) -------
+
+def split_list(args, lens):
+    """Cut ``args`` into consecutive pieces of the given lengths."""
+    out, pos = [], 0
+    for n in lens:
+        out.append(args[pos:pos + n])
+        pos += n
+    assert pos == len(args), f"expected {pos} arguments, got {len(args)}"
+    return out
+
+
+def get_meta(tensors):
+    return tuple((t.shape, t.stride(), t.dtype) for t in tensors)
+
+
+def verify_meta(a, b, msg=""):
+    """Shapes, dtypes and strides (of dims larger than 1) of ``a`` must equal ``b``'s."""
+    for i, (x, y) in enumerate(zip(a, b)):
+        assert x.shape == y.shape, msg + f"#{i + 1}: shape {tuple(x.shape)} != {tuple(y.shape)}"
+        sx = [s if n > 1 else 0 for s, n in zip(x.stride(), x.shape)]
+        sy = [s if n > 1 else 0 for s, n in zip(y.stride(), y.shape)]
+        assert sx == sy, msg + f"#{i + 1}: stride {sx} != {sy}"
+        assert x.dtype == y.dtype, msg + f"#{i + 1}: dtype {x.dtype} != {y.dtype}"
+
+
+# -- tunables -------------------------------------------------------------------
+
+@dataclass
+class Tuning:
+    """Code-generation parameters (defaults picked by ``default_tuning``)."""
+    fw_r: int = 4
+    fw_c: int = 16
+    fw_mb: int = 32
+    fw_stage: int = 16
+    fw_min_blocks: int = 1
+    bw_r: int = 8
+    bw_c: int = 8
+    seg: int = 4
+    nslots: int = 2
+    use_tma: bool = True
+
+
+SMEM_LIMIT = 227 * 1024
+
+
+def default_tuning(B, T, H, M, N, nstates) -> Tuning:
+    tu = Tuning()
+    for k, v in os.environ.items():
+        if k.startswith("FRNN_TUNE_"):
+            f = k[len("FRNN_TUNE_"):].lower()
+            if hasattr(tu, f):
+                setattr(tu, f, type(getattr(tu, f))(int(v)))
+    slot = M * N * 4 * nstates
+    # checkpoint chunk = seg * nslots steps, bounded by T and by shared memory for the slots
+    while tu.nslots > 1 and max(tu.nslots, 2) * slot > 160 * 1024:
+        tu.nslots -= 1
+    while tu.seg * tu.nslots > T and tu.nslots > 1:
+        tu.nslots -= 1
+    while tu.seg * tu.nslots > T and tu.seg > 1:
+        tu.seg -= 1
+    tu.fw_stage = max(1, min(tu.fw_stage, T))
+    return tu
+
+
+# -- the planner -----------------------------------------------------------------
+
+@dataclass
+class Plan:
+    problem: Problem
+    joint: StepGraph
+    g_fw: StepGraph
+    g_re: StepGraph
+    g_bw: StepGraph
+    aux: List[str]
+    n_out: int
+    n_st: int
+    grads: List[GradOut]
+    tuning: Tuning
+    fw_tile: lower.Tile
+    bw_tile: lower.Tile
+    D: int
+    nck: int
+    k_fwd: int
+    k_joint: int
+
+
+def _spec(t: th.Tensor) -> TensorSpec:
+    ptr_ok = True
+    if t.device.type == "cuda":
+        ptr_ok = t.data_ptr() % 16 == 0
+    return TensorSpec(tuple(t.shape), tuple(t.stride()), _DT[t.dtype], ptr_ok)
+
+
+def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Tensor],
+              tuning: Optional[Tuning] = None) -> Tuple[Plan, tuple, tuple]:
+    inputs, state = tuple(inputs), tuple(state)
+    assert len(state) >= 1, "a step function needs at least one state"
+    B, T, H = [max(i.shape[j] for i in inputs) for j in range(3)] if inputs else (state[0].shape[0], 1, state[0].shape[1])
+    M = max(i.shape[-2] for i in inputs + state)
+    N = max(i.shape[-1] for i in inputs + state)
+    full = [B, T, H, M, N]
+    for i, x in enumerate(inputs):
+        assert x.ndim == 5, f"invalid shape {list(x.shape)} of argument #{i + 1}"
+        for j in range(5):
+            assert x.shape[j] in (1, full[j]), f"shape {list(x.shape)} of argument #{i + 1} is incompatible with {full}"
+        assert 1 in x.shape[-2:] or x.shape[1] == 1, (
+            f"shape {list(x.shape)} of argument #{i + 1} is both a matrix for each head, and depends on time. This is not supported")
+        assert x.dtype in _IO_DTYPES, f"unsupported dtype {x.dtype} of argument #{i + 1}"
+    for i, x in enumerate(state):
+        assert list(x.shape) == [B, H, M, N], f"shape {list(x.shape)} of argument #{i + 1 + len(inputs)} != {[B, H, M, N]}"
+        assert x.dtype in _IO_DTYPES, f"unsupported dtype {x.dtype} of argument #{i + 1 + len(inputs)}"
+    nin, nst = len(inputs), len(state)
+
+    # output arity and dtypes: run the step on meta tensors of the original dtypes
+    with th.utils._python_dispatch._disable_current_modes():
+        metas = [th.empty(B, H, *x.shape[-2:], dtype=x.dtype, device="meta") for x in inputs] + \
+                [th.empty(x.shape, dtype=x.dtype, device="meta") for x in state]
+        y_t, s_t = step(*metas)
+        y_t, s_t = as_tuple(y_t), as_tuple(s_t)
+    assert len(s_t) == nst, f"step returns {len(s_t)} states but was given {nst}"
+    assert all(tuple(a.shape) == (B, H, M, N) for a in s_t), "new states must have the shape of the states"
+    assert all(list(o.shape) == [B, H, M, 1] for o in y_t), [tuple(o.shape) for o in y_t]
+    assert all(o.dtype in _IO_DTYPES for o in y_t)
+    nout = len(y_t)
+    out_dtypes = [o.dtype for o in y_t]
+
+    in_cls = [(int(x.shape[3] > 1), int(x.shape[4] > 1)) for x in inputs]
+    st_cls = (int(M > 1), int(N > 1))
+    joint, no2, ns2 = trace_joint(step, in_cls + [st_cls] * nst, nin, has_m=M > 1, has_n=N > 1)
+    assert (no2, ns2) == (nout, nst)
+    jin = joint.inputs
+    in_names, st_names = jin[:nin], jin[nin:nin + nst]
+    dy_names, dnext_names = jin[nin + nst:nin + nst + nout], jin[nin + nst + nout:]
+    jout = joint.outputs
+    y_names, ns_names = jout[:nout], jout[nout:nout + nst]
+    dx_names, ds_names = jout[nout + nst:nout + nst + nin], jout[nout + nst + nin:]
+
+    # forward must not depend on the cotangents
+    cot = joint.depends_on(dy_names + dnext_names)
+    g_fw0 = joint.pruned(y_names + ns_names, "step")
+    assert not any(n.name in cot for n in g_fw0.nodes)
+    # aux: forward row sums of [M,N] operands that the backward (or the re-step) reads
+    cands = [n.name for n in joint.nodes
+             if n.op == "sum" and n.over_n and not n.over_m and joint.shape[n.args[0]] == MN and n.name not in cot]
+    probe = joint.pruned(ns_names + dx_names + ds_names, "probe", leaves=cands)
+    aux = [c for c in cands if c in probe.inputs]
+    g_fw = joint.pruned(y_names + ns_names + aux, "step")
+    g_fw.inputs = jin[:nin + nst]
+    g_re = joint.pruned(ns_names, "restep", leaves=aux)
+    g_bw = joint.pruned(dx_names + ds_names, "dstep", leaves=aux)
+    for n in g_fw.nodes:
+        if n.op == "sum" and n.over_m:
+            raise AssertionError("Only torch.sum(x, dim=-1, keepdim=True) is supported")
+
+    tu = tuning or default_tuning(B, T, H, M, N, nst)
+    fw_tile = choose_tile(M, N, tu.fw_r, tu.fw_c, tu.fw_mb)
+    bw_tile = choose_tile(M, N, tu.bw_r, tu.bw_c, None)
+    D = tu.seg * tu.nslots
+    nck = (T + D - 1) // D
+
+    dev = inputs[0].device if inputs else state[0].device
+    # declared outputs (what the fake implementations materialise)
+    out_meta = tuple(th.empty(B, T, H, M, dtype=d, device="meta") for d in out_dtypes)
+    stT_meta = tuple(th.empty_like(s, device="meta") for s in state)
+    store_meta = tuple(th.empty(B, H, nck, M, N, dtype=th.float32, device="meta") for _ in state)
+    aux_meta = (th.empty(len(aux), B, H, T, M, dtype=th.float32, device="meta"),)
+    dx_meta = tuple(th.empty_like(x, device="meta") for x in inputs)
+    fw_meta = get_meta([*out_meta, *stT_meta, *store_meta, *aux_meta])
+    bw_meta = get_meta([*dx_meta, *stT_meta])
+
+    grads: List[GradOut] = []
+    for i, x in enumerate(inputs):
+        cls = in_cls[i]
+        atomic = list(x.shape[:3]) != [B, T, H]
+        over_t = x.shape[1] == 1 and T > 1
+        gm = dx_meta[i]
+        if atomic:
+            spec = TensorSpec(tuple(gm.shape), tuple(th.empty(gm.shape, device="meta").stride()), DT_F32, True)
+        else:
+            spec = TensorSpec(tuple(gm.shape), tuple(gm.stride()), _DT[gm.dtype], True)
+        grads.append(GradOut(i, cls, spec, dx_names[i], over_t, atomic))
+
+    prob = Problem(B, T, H, M, N, [_spec(x) for x in inputs], list(in_names), [_spec(s) for s in state],
+                   list(st_names), [_DT[d] for d in out_dtypes], len(aux))
+    plan = Plan(prob, joint, g_fw, g_re, g_bw, aux, nout, nst, grads, tu, fw_tile, bw_tile, D, nck,
+                g_fw0.count_mn_ops(), joint.pruned(jout, "all").count_mn_ops())
+    plan.dy_names, plan.dnext_names = list(dy_names), list(dnext_names)   # type: ignore[attr-defined]
+    return plan, fw_meta, bw_meta
+
+
+def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
+    """Emit the CUDA source of the forward and the backward kernel."""
+    p, tu = plan.problem, plan.tuning
+    fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, plan.fw_tile, tu.fw_stage, plan.D, tu.use_tma,
+                      tu.fw_min_blocks, prelude())
+    if any(g.cls == MN for g in plan.grads):
+        raise lower.LoweringError("matrix-per-head inputs are not supported yet")
+    bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, [], plan.dy_names,   # type: ignore[attr-defined]
+                       plan.dnext_names, plan.bw_tile, tu.seg, tu.nslots, tu.use_tma, prelude())          # type: ignore[attr-defined]
+    for k in (fw, bw):
+        if k.smem_bytes > SMEM_LIMIT:
+            raise lower.LoweringError(f"kernel {k.name} needs {k.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
+    return fw, bw
+
+
+class _CudaLauncher:
+    """Compiles a generated kernel with NVRTC and launches it through the
+    C-ABI library on the current stream of the tensors' device."""
+
+    def __init__(self, ks: lower.KernelSource):
+        from . import runtime
+        self.rt, self.ks = runtime, ks
+        self.mods: Dict[int, object] = {}
+        self.log = ""
+
+    def __call__(self, ptrs, device: th.device):
+        idx = device.index if device.index is not None else th.cuda.current_device()
+        with th.cuda.device(idx):
+            if idx not in self.mods:
+                cubin, self.log = self.rt.compile_cubin(self.ks.source)
+                self.mods[idx] = self.rt.Module(cubin, [self.ks.name], [self.ks.smem_bytes])
+            self.mods[idx].launch(0, self.ks.grid, self.ks.block, self.ks.smem_bytes,
+                                  th.cuda.current_stream(idx).cuda_stream, ptrs)
+
+
+class _device_ctx:
+    def __init__(self, device):
+        self.ctx = th.cuda.device(device) if device.type == "cuda" else None
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *a):
+        if self.ctx is not None:
+            self.ctx.__exit__(*a)
+
+
+def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = None, _launcher=None):
+    """See the module docstring.  With ``dryrun`` nothing touches CUDA.
+
+    ``_launcher`` is a seam for the test-suite only: a factory
+    ``KernelSource -> callable(ptrs, device)`` that stands in for the NVRTC +
+    C-ABI launch (the tests inject a host emulation of the generated source to
+    check it without a GPU).  Library code never passes it, and without it
+    tensors that are not on a CUDA device are rejected.
+    """
+    plan, fw_meta, bw_meta = make_plan(step, inputs, state, tuning)
+    if dryrun:
+        return fw_meta, bw_meta
+
+    inputs, state = tuple(inputs), tuple(state)
+    dev = inputs[0].device if inputs else state[0].device
+    if dev.type != "cuda" and _launcher is None:
+        raise RuntimeError("flex_rnn_b200 runs on CUDA devices only (there is no CPU path); "
+                           "use the .naive method for a CPU evaluation of the step function")
+    fw_src, bw_src = generate(plan)
+    p = plan.problem
+    nin, nst, nout = len(inputs), plan.n_st, plan.n_out
+    make = _launcher or _CudaLauncher
+    launch_fw, launch_bw = make(fw_src), make(bw_src)
+
+    in_meta = tuple(th.empty_strided(x.shape, x.stride(), dtype=x.dtype, device="meta") for x in inputs)
+    st_meta = tuple(th.empty_strided(x.shape, x.stride(), dtype=x.dtype, device="meta") for x in state)
+    in_align = [x.data_ptr() % 16 == 0 for x in inputs]
+    st_align = [x.data_ptr() % 16 == 0 for x in state]
+    fw_used = plan.g_fw.used_inputs()
+    bw_used = [a or b for a, b in zip(plan.g_re.used_inputs(), plan.g_bw.used_inputs())]
+    err_words: Dict[int, th.Tensor] = {}
+
+    def err_word(device):
+        idx = device.index
+        if idx not in err_words:
+            err_words[idx] = th.zeros(1, dtype=th.int32, device=device)
+        return err_words[idx]
+
+    def check_align(ts, flags, what):
+        for i, (t, f) in enumerate(zip(ts, flags)):
+            assert (t.data_ptr() % 16 == 0) or not f, (
+                f"{what} #{i + 1} was 16-byte aligned at compilation but is not now")
+
+    def forward(inputs_, state0):
+        verify_meta(inputs_, in_meta, "input Tensor metadata doesn't match compilation\n")
+        verify_meta(state0, st_meta, "initial state Tensor metadata doesn't match compilation\n")
+        check_align(inputs_, in_align, "input")
+        check_align(state0, st_align, "initial state")
+        device = inputs_[0].device
+        with _device_ctx(device):
+            outs = tuple(th.empty(p.B, p.T, p.H, p.M, dtype=d, device=device)
+                         for d in [o[2] for o in fw_meta[:nout]])
+            stT = tuple(th.empty_like(s) for s in state0)
+            store = tuple(th.empty(p.B, p.H, plan.nck, p.M, p.N, dtype=th.float32, device=device) for _ in state0)
+            aux = th.empty(len(plan.aux), p.B, p.H, p.T, p.M, dtype=th.float32, device=device)
+            ew = err_word(device)
+            ptrs = [x.data_ptr() for x, u in zip(inputs_, fw_used[:nin]) if u]
+            ptrs += [s.data_ptr() for s in state0] + [o.data_ptr() for o in outs] + [s.data_ptr() for s in stT]
+            ptrs += [s.data_ptr() for s in store] + [aux.data_ptr(), ew.data_ptr()]
+            launch_fw(ptrs, device)
+        return (*outs, *stT, *store, aux)
+
+    def backward(doutput, dstateT, inputs_, state_store, aux_):
+        doutput = tuple(d.contiguous() for d in doutput)
+        dstateT = tuple(d.contiguous() for d in dstateT)
+        verify_meta(inputs_, in_meta)
+        check_align(inputs_, in_align, "input")
+        aux = aux_[0] if isinstance(aux_, (tuple, list)) else aux_
+        device = inputs_[0].device
+        with _device_ctx(device):
+            dxs = []
+            for go, x in zip(plan.grads, inputs_):
+                if go.atomic:
+                    dxs.append(th.zeros(x.shape, dtype=th.float32, device=device))
+                else:
+                    dxs.append(th.empty_like(x))
+            ds0 = tuple(th.empty_strided(m.shape, m.stride(), dtype=m.dtype, device=device) for m in
+                        (th.empty_like(s, device="meta") for s in st_meta))
+            ew = err_word(device)
+            ptrs = [x.data_ptr() for x, u in zip(inputs_, bw_used[:nin]) if u]
+            ptrs += [d.data_ptr() for d in doutput] + [d.data_ptr() for d in dstateT]
+            ptrs += [s.data_ptr() for s in state_store] + [aux.data_ptr()]
+            ptrs += [d.data_ptr() for d in ds0] + [d.data_ptr() for d in dxs] + [ew.data_ptr()]
+            launch_bw(ptrs, device)
+            for i, go in enumerate(plan.grads):
+                if go.atomic:
+                    dxs[i] = dxs[i].to(inputs_[i].dtype)
+        return tuple(dxs), ds0
+
+    def kernel_status(device=None) -> int:
+        """Error word the kernels write on a timed-out wait (0 = none). Synchronises."""
+        device = th.device(device) if device is not None else dev
+        if device.index not in err_words:
+            return 0
+        return int(err_words[device.index].item())
+
+    forward.plan = plan                     # type: ignore[attr-defined]
+    forward.sources = (fw_src, bw_src)      # type: ignore[attr-defined]
+    forward.launchers = (launch_fw, launch_bw)   # type: ignore[attr-defined]
+    forward.kernel_status = kernel_status   # type: ignore[attr-defined]
+    return forward, backward, fw_meta, bw_meta

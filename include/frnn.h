@@ -1,0 +1,104 @@
+/*
+ * frnn.h - C ABI of libfrnn_b200.so, the launch boundary of the B200 backend
+ * for flex_rnn step functions.
+ *
+ * In the reference project the generated CUDA is wrapped, per compiled step,
+ * in host stubs `void <kernel>_(void* ...)` that launch with a baked
+ * `<<<grid, block>>>` on the legacy default stream, and those stubs are bound
+ * as torch ops taking tensors and passing `data_ptr()`
+ * (flex_rnn/to_cuda.py:230-280: `build_cuda`).  This library is what replaces
+ * that boundary: the generated source is compiled at run time with NVRTC for
+ * sm_100a and launched on a caller-supplied stream through the functions
+ * below.  Plain pointers and sizes only; no torch types cross this boundary.
+ *
+ * Conventions: every function returns 0 on success and a non-zero FRNN_E_*
+ * code on failure; nothing throws; `frnn_last_error()` gives a per-thread
+ * message for the last failure.  The caller owns every device buffer; kernels
+ * only read their inputs and write the buffers passed as outputs.  All calls
+ * are thread-safe.  A module belongs to the device that was current when it
+ * was loaded.
+ */
+#ifndef FRNN_H
+#define FRNN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    FRNN_OK = 0,
+    FRNN_E_ARG = 1,        /* bad argument */
+    FRNN_E_NVRTC = 2,      /* NVRTC missing or compilation failed (see log) */
+    FRNN_E_DRIVER = 3,     /* CUDA driver missing or a driver call failed */
+    FRNN_E_LAUNCH = 4,     /* launch rejected (resources, configuration) */
+    FRNN_E_KERNEL = 5      /* a kernel reported an error through its error word */
+};
+
+typedef struct frnn_module* frnn_module_t;
+
+/* Version of this ABI (bumped on any signature change). */
+int frnn_abi_version(void);
+
+/* Message for the calling thread's most recent failure ("" if none). */
+const char* frnn_last_error(void);
+
+/*
+ * Compile CUDA C++ `src` to an sm_100a cubin with NVRTC (no GPU needed).
+ * Replaces the nvcc+ninja build of flex_rnn/to_cuda.py:274-279.
+ * `opts`: extra NVRTC options (may be NULL when nopts == 0).
+ * On success *cubin is a malloc'd buffer of *cubin_size bytes that the caller
+ * releases with frnn_free().  `log` (may be NULL) receives the NUL-terminated
+ * compiler log, truncated to log_cap bytes; it holds the ptxas resource usage
+ * (registers, spills, shared memory) of every kernel.
+ */
+int frnn_compile(const char* src, const char* const* opts, int nopts,
+                 void** cubin, size_t* cubin_size, char* log, size_t log_cap);
+
+void frnn_free(void* p);
+
+/*
+ * Load a cubin on the current device and look up `nkernels` entry points by
+ * name.  Replaces the dlopen of the extension built by to_cuda.py:279-280.
+ * Raises each kernel's dynamic shared memory limit to `smem_bytes[i]`.
+ */
+int frnn_module_load(const void* cubin, size_t cubin_size,
+                     const char* const* kernel_names, const unsigned* smem_bytes,
+                     int nkernels, frnn_module_t* out);
+
+int frnn_module_unload(frnn_module_t m);
+
+/*
+ * Launch kernel `kernel` of module `m` on `stream` (a cudaStream_t / CUstream;
+ * NULL = default stream).  `args[i]` points at the i-th kernel parameter value
+ * (for a pointer parameter: the address of a variable holding the device
+ * pointer), as for cuLaunchKernel.  Replaces the `<<<grid, block>>>` stubs of
+ * flex_rnn/to_cuda.py:245-247, adding the stream argument and error checking
+ * that those stubs lack.  Asynchronous: returns once the launch is enqueued.
+ */
+int frnn_launch(frnn_module_t m, int kernel, const unsigned grid[3], const unsigned block[3],
+                unsigned smem_bytes, void* stream, void* const* args, int nargs);
+
+/* Registers per thread, static shared bytes and local (spill) bytes per thread
+ * of a loaded kernel, as the driver reports them. */
+int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, int* local_bytes);
+
+/* ---- helpers compiled into the library (used by the benchmark harness) ---- */
+
+/* Overwrite `bytes` bytes at `buf` (device) with a byte pattern; writing a
+ * buffer larger than L2 between timed iterations evicts the previous
+ * iteration's data. */
+int frnn_l2_flush(void* buf, size_t bytes, void* stream);
+
+/* Run an FMA-only register-resident loop on every SM for `iters` iterations and
+ * return the floating point operations it performs in *flops (2 per FMA).
+ * Timed by the caller with events, it measures the FP32 CUDA-core peak that
+ * bounds the recurrent kernels.  `sink` is a device buffer of >= 4 bytes. */
+int frnn_fp32_peak_probe(float* sink, int iters, void* stream, double* flops);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRNN_H */

@@ -1,0 +1,60 @@
+"""Compile a generated kernel with g++ against frnn_emu.h and run it on CPU tensors.
+
+Used by the CPU tests to check the generated source itself (index arithmetic,
+graph lowering, reductions, staging, checkpoint/recompute schedule) against the
+oracle without a GPU.  Test infrastructure only.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import subprocess
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_CACHE = os.path.join(tempfile.gettempdir(), "frnn_emu_cache")
+
+
+def _wrapper(ks) -> str:
+    casts = []
+    for i, d in enumerate(ks.param_decl):
+        ctype = d.rsplit(" ", 1)[0].replace("__restrict__", "")
+        casts.append(f"({ctype})args[{i}]")
+    return (f'\nextern "C" void emu_run_{ks.name}(const unsigned* grid, unsigned nthreads, unsigned smem, void** args) {{\n'
+            f"  emu_launch([](void** args) {{ {ks.name}({', '.join(casts)}); }}, grid, nthreads, smem, args);\n}}\n")
+
+
+def compile_emu(ks):
+    os.makedirs(_CACHE, exist_ok=True)
+    src = '#include <cstdio>\n#include "frnn_emu.h"\n' + ks.source + _wrapper(ks)
+    key = hashlib.sha256((src + open(os.path.join(HERE, "frnn_emu.h")).read()).encode()).hexdigest()[:24]
+    so = os.path.join(_CACHE, f"emu_{key}.so")
+    if not os.path.exists(so):
+        cpp = os.path.join(_CACHE, f"emu_{key}.cpp")
+        with open(cpp, "w") as f:
+            f.write(src)
+        cmd = ["g++", "-std=c++20", "-O1", "-shared", "-fPIC", "-pthread", "-Wno-unknown-pragmas", "-Wno-attributes",
+               "-I", HERE, "-o", so + ".tmp", cpp]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            raise RuntimeError("emulation build failed:\n" + r.stderr[-4000:])
+        os.replace(so + ".tmp", so)
+    return ctypes.CDLL(so)
+
+
+class EmuLauncher:
+    """Drop-in for the CUDA launcher of ``build_twopass`` (its ``_launcher`` seam)."""
+
+    def __init__(self, ks):
+        self.ks = ks
+        self.lib = compile_emu(ks)
+        self.fn = getattr(self.lib, f"emu_run_{ks.name}")
+        self.fn.argtypes = [ctypes.POINTER(ctypes.c_uint), ctypes.c_uint, ctypes.c_uint, ctypes.POINTER(ctypes.c_void_p)]
+        self.fn.restype = None
+
+    def __call__(self, ptrs, device=None):
+        n = len(ptrs)
+        args = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(p)) for p in ptrs])
+        grid = (ctypes.c_uint * 3)(*self.ks.grid)
+        self.fn(grid, self.ks.block, self.ks.smem_bytes, args)

@@ -1,0 +1,143 @@
+// Host emulation of the few CUDA facilities the generated recurrent kernels
+// use, so that the *same generated source* can be compiled with g++ and run on
+// the CPU by the test-suite: one OS thread per CUDA thread, std::barrier for
+// __syncthreads / warp sync, an exchange buffer for shuffles, memcpy + a
+// counter for the TMA bulk copy and its mbarrier.  Test infrastructure only:
+// nothing in the library imports or runs this.
+#pragma once
+#define FRNN_EMU 1
+#include <atomic>
+#include <barrier>
+#include <chrono>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <algorithm>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+typedef unsigned short u16;
+typedef unsigned int u32;
+typedef unsigned long long u64;
+using std::min;
+using std::max;
+
+#define FRNN_DEV inline
+#define __global__
+#define __restrict__
+#define __launch_bounds__(...)
+#define __align__(n) alignas(n)
+
+struct emu_dim3 { unsigned x = 0, y = 0, z = 0; };
+struct emu_cta {
+    int nthreads;
+    std::barrier<>* block_bar;
+    std::vector<std::barrier<>*> warp_bar;
+    std::vector<float> xchg;          // [nthreads]
+    unsigned char* smem;
+    std::mutex mtx;
+};
+static thread_local emu_dim3 threadIdx, blockIdx;
+static thread_local emu_cta* emu_ctx = nullptr;
+static std::mutex emu_atomic_mtx;
+
+#define FRNN_DYN_SMEM(name) unsigned char* name = emu_ctx->smem
+
+FRNN_DEV float emu_u2f(u32 v) { float f; memcpy(&f, &v, 4); return f; }
+FRNN_DEV u32 emu_f2u(float f) { u32 v; memcpy(&v, &f, 4); return v; }
+FRNN_DEV float frnn_bf16_to_f32(u16 v) { return emu_u2f(((u32)v) << 16); }
+FRNN_DEV u16 frnn_f32_to_bf16(float f) {
+    u32 x = emu_f2u(f);
+    if ((x & 0x7fffffffu) > 0x7f800000u) return (u16)((x >> 16) | 0x40);  // NaN
+    u32 lsb = (x >> 16) & 1u;
+    x += 0x7fffu + lsb;
+    return (u16)(x >> 16);
+}
+FRNN_DEV float frnn_f16_to_f32(u16 v) { _Float16 h; memcpy(&h, &v, 2); return (float)h; }
+FRNN_DEV u16 frnn_f32_to_f16(float f) { _Float16 h = (_Float16)f; u16 v; memcpy(&v, &h, 2); return v; }
+
+FRNN_DEV u64 frnn_now_ns() {
+    return (u64)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// mbarrier emulation inside the 8 bytes: [phase:16 | arrived:16 | pending:32 (signed)]
+struct emu_mbar { int pending; unsigned short arrived; unsigned short phase; };
+static_assert(sizeof(emu_mbar) == 8, "mbarrier emulation must fit the 64-bit word");
+FRNN_DEV void emu_mbar_settle(emu_mbar* b) {
+    if (b->arrived && b->pending == 0) { b->phase++; b->arrived = 0; }
+}
+FRNN_DEV void frnn_mbar_init(u64* bar, u32) { emu_mbar* b = (emu_mbar*)bar; b->pending = 0; b->arrived = 0; b->phase = 0; }
+FRNN_DEV void frnn_mbar_init_fence() {}
+FRNN_DEV void frnn_async_proxy_fence() {}
+FRNN_DEV void frnn_mbar_expect_tx(u64* bar, u32 bytes) {
+    std::lock_guard<std::mutex> g(emu_ctx->mtx);
+    emu_mbar* b = (emu_mbar*)bar;
+    b->pending += (int)bytes; b->arrived = 1; emu_mbar_settle(b);
+}
+FRNN_DEV void frnn_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+    if (((uintptr_t)dst & 15) || ((uintptr_t)src & 15) || (bytes & 15)) {
+        fprintf(stderr, "emu: misaligned bulk copy dst=%p src=%p bytes=%u\n", dst, src, bytes); abort();
+    }
+    memcpy(dst, src, bytes);
+    std::lock_guard<std::mutex> g(emu_ctx->mtx);
+    emu_mbar* b = (emu_mbar*)bar;
+    b->pending -= (int)bytes; emu_mbar_settle(b);
+}
+FRNN_DEV bool frnn_mbar_try(u64* bar, u32 parity) {
+    std::lock_guard<std::mutex> g(emu_ctx->mtx);
+    emu_mbar* b = (emu_mbar*)bar;
+    bool ok = ((b->phase & 1u) != parity);
+    if (!ok) std::this_thread::yield();
+    return ok;
+}
+FRNN_DEV float frnn_shfl_xor(float v, int off) {
+    emu_cta* c = emu_ctx;
+    int tid = threadIdx.x, w = tid >> 5;
+    c->xchg[tid] = v;
+    c->warp_bar[w]->arrive_and_wait();
+    float r = c->xchg[tid ^ off];
+    c->warp_bar[w]->arrive_and_wait();
+    return r;
+}
+FRNN_DEV void frnn_block_sync() { emu_ctx->block_bar->arrive_and_wait(); }
+FRNN_DEV void frnn_warp_sync() { emu_ctx->warp_bar[threadIdx.x >> 5]->arrive_and_wait(); }
+FRNN_DEV void frnn_atomic_add(float* p, float v) { std::lock_guard<std::mutex> g(emu_atomic_mtx); *p += v; }
+FRNN_DEV void frnn_report(int* err, int code) { std::lock_guard<std::mutex> g(emu_atomic_mtx); if (*err == 0) *err = code; }
+FRNN_DEV float frnn_expf(float x) { return std::exp(x); }
+FRNN_DEV float frnn_logf(float x) { return std::log(x); }
+FRNN_DEV float frnn_sqrtf(float x) { return std::sqrt(x); }
+FRNN_DEV float frnn_rcpf(float x) { return 1.0f / x; }
+FRNN_DEV float frnn_divf(float a, float b) { return a / b; }
+
+// ---- launcher -------------------------------------------------------------------
+typedef void (*emu_entry_t)(void** args);
+static void emu_launch(emu_entry_t fn, const unsigned grid[3], unsigned nthreads, unsigned smem_bytes, void** args) {
+    for (unsigned bz = 0; bz < grid[2]; bz++)
+        for (unsigned by = 0; by < grid[1]; by++)
+            for (unsigned bx = 0; bx < grid[0]; bx++) {
+                emu_cta cta;
+                cta.nthreads = (int)nthreads;
+                std::barrier<> bb((std::ptrdiff_t)nthreads);
+                cta.block_bar = &bb;
+                std::vector<std::barrier<>*> wb;
+                for (unsigned w = 0; w < (nthreads + 31) / 32; w++)
+                    wb.push_back(new std::barrier<>((std::ptrdiff_t)std::min(32u, nthreads - w * 32)));
+                cta.warp_bar = wb;
+                cta.xchg.assign(nthreads, 0.f);
+                unsigned char* raw = (unsigned char*)aligned_alloc(128, ((size_t)smem_bytes + 255) / 128 * 128);
+                memset(raw, 0xCD, smem_bytes);
+                cta.smem = raw;
+                std::vector<std::thread> th;
+                for (unsigned t = 0; t < nthreads; t++)
+                    th.emplace_back([&, t] {
+                        threadIdx.x = t; threadIdx.y = threadIdx.z = 0;
+                        blockIdx.x = bx; blockIdx.y = by; blockIdx.z = bz;
+                        emu_ctx = &cta;
+                        fn(args);
+                    });
+                for (auto& t : th) t.join();
+                for (auto* b : wb) delete b;
+                free(raw);
+            }
+}
