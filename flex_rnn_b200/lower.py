@@ -103,15 +103,17 @@ def choose_tile(M: int, N: int, want_r: int, want_c: int, want_mb: Optional[int]
             R *= 2
         else:
             raise LoweringError("cannot fit the row tile in one CTA")
-    while ((MB // R) * L) % 32:
+    while ((MB // R) * (N // C)) % 32:
         if R > 1:
             R //= 2
         elif MB < M:
             MB = min(M, MB * 2)
             while M % MB:
                 MB += 1
+        elif C > 1 and N // (C // 2) <= 32:
+            C //= 2
         else:
-            raise LoweringError(f"state {M}x{N} is too small for a 32-thread CTA with this tile")
+            raise LoweringError(f"state {M}x{N} is too small for a 32-thread CTA")
     return Tile(R, C, MB, M, N)
 
 
@@ -342,6 +344,7 @@ class Body:
             rs = "r" if n.shape[0] else "0"
             cs = "c" if n.shape[1] else "0"
             # outer loops over the kept dims, inner accumulation over the reduced dims
+            w.open("")
             if n.shape[0]:
                 w("#pragma unroll")
                 w.open(f"for (int r = 0; r < {t.R}; r++)")
@@ -367,6 +370,7 @@ class Body:
                 w.close()
             if n.shape[0]:
                 w.close()
+            w.close()
             return
         self.partial[n.name] = self._check_partial(n)
         self.declare(n.name, n.shape)
@@ -831,7 +835,7 @@ class GradOut:
 def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[str], n_out: int,
                   grads: List[GradOut], dstate_names: List[str], dy_names: List[str],
                   dnext_names: List[str], tile: Tile, seg: int, nslots: int, use_tma: bool,
-                  prelude: str, kname: str = "frnn_bw") -> KernelSource:
+                  prelude: str, kname: str = "frnn_bw", red_bufs: int = 2) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -899,7 +903,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     pm_sc = [go for go in grads if go.cls == S11]
     redw = len(pm_vec) * p.N + len(pm_sc)
     redw_pad = (redw + 3) // 4 * 4
-    red_bytes = 2 * t.RG * redw_pad * 4 if redw else 0
+    red_bytes = red_bufs * t.RG * redw_pad * 4 if redw else 0
     nphys = max(nslots, 2)
     slot_elems = p.M * p.N
     slot_bytes = slot_elems * 4
@@ -1087,6 +1091,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                                   atomic=go.atomic)
     # per-column / per-head gradient partials -> exchange buffer
     if redw:
+        if red_bufs == 1:
+            w("frnn_block_sync();   // single exchange buffer: the previous step's readers must be done")
         w(f"float* rb = red + rpar * {t.RG * redw_pad} + rg * {redw_pad};")
         for vi, go in enumerate(pm_vec):
             val = go.value
@@ -1143,7 +1149,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             lo += n_el
         w.close()
         w.close()
-        w("rpar ^= 1;")
+        if red_bufs == 2:
+            w("rpar ^= 1;")
     w.close()   # backward step scope
     w.close()   # i loop
     w.close()   # if j < nseg

@@ -243,8 +243,13 @@ def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
                       tu.fw_min_blocks, prelude())
     if any(g.cls == MN for g in plan.grads):
         raise lower.LoweringError("matrix-per-head inputs are not supported yet")
-    bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, [], plan.dy_names,   # type: ignore[attr-defined]
-                       plan.dnext_names, plan.bw_tile, tu.seg, tu.nslots, tu.use_tma, prelude())          # type: ignore[attr-defined]
+    bw = None
+    for red_bufs in (2, 1):
+        bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, [], plan.dy_names,   # type: ignore[attr-defined]
+                           plan.dnext_names, plan.bw_tile, tu.seg, tu.nslots, tu.use_tma, prelude(),        # type: ignore[attr-defined]
+                           red_bufs=red_bufs)
+        if bw.smem_bytes <= SMEM_LIMIT:
+            break
     for k in (fw, bw):
         if k.smem_bytes > SMEM_LIMIT:
             raise lower.LoweringError(f"kernel {k.name} needs {k.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
