@@ -4,8 +4,10 @@ The reference obtains the joint graph with ``functorch.compile.aot_function``
 and, when a fake-tensor mode is active (that is, under ``torch.compile``),
 re-runs the trace in a child process (flex_rnn/trace_isolated.py:3-39 in the
 reference project).  Here the joint function ``(x, dy) -> (y, vjp(dy))`` is
-traced in-process with ``make_fx`` on meta tensors; an active fake / dispatch
-mode is suspended for the duration of the trace, so no child process is needed.
+traced in-process with ``make_fx`` on meta tensors.  For the duration of the
+trace the dispatcher is put back into its plain eager state (active fake /
+proxy modes suspended, the "below autograd" key exclusion that surrounds a
+custom op's fake implementation lifted), so no child process is needed.
 """
 from __future__ import annotations
 
@@ -17,6 +19,9 @@ from torch.utils._python_dispatch import _disable_current_modes
 
 from .graph import StepGraph, from_fx
 
+_TLS_INCLUDE = torch._C._dispatch_tls_local_include_set()
+_TLS_EXCLUDE = torch._C._dispatch_tls_local_exclude_set()
+
 #: stand-in sizes used while tracing; distinct and > 1 so that a traced
 #: value's shape tells whether it varies over rows and/or columns
 TRACE_M, TRACE_N = 3, 5
@@ -26,8 +31,38 @@ def as_tuple(x):
     return tuple(x) if isinstance(x, (tuple, list)) else (x,)
 
 
+class clean_dispatch:
+    """Context manager giving the dispatcher state of plain eager code: active
+    fake / proxy modes are suspended and the thread-local dispatch-key sets are
+    forced back to the values recorded when this module was imported (a custom
+    op's fake implementation runs "below autograd", where ``torch.func.vjp``
+    cannot work)."""
+
+    def __enter__(self):
+        self._a = torch._C._ForceDispatchKeyGuard(_TLS_INCLUDE, _TLS_EXCLUDE)
+        self._b = _disable_current_modes()
+        self._a.__enter__()
+        self._b.__enter__()
+
+    def __exit__(self, *exc):
+        self._b.__exit__(*exc)
+        self._a.__exit__(*exc)
+
+
+def run_isolated(fn, *args):
+    """Run ``fn(*args)`` with clean dispatcher state."""
+    with clean_dispatch():
+        return fn(*args)
+
+
 def trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: int,
                 has_m: bool = True, has_n: bool = True) -> Tuple[StepGraph, int, int]:
+    with clean_dispatch():
+        return _trace_joint(step, classes, n_inputs, has_m, has_n)
+
+
+def _trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: int,
+                 has_m: bool = True, has_n: bool = True) -> Tuple[StepGraph, int, int]:
     """Trace ``step`` on per-head tiles.
 
     ``classes[i]`` is ``(over_m, over_n)`` of argument ``i`` (inputs first, then
@@ -38,7 +73,7 @@ def trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: in
     """
     tm = TRACE_M if has_m else 1
     tn = TRACE_N if has_n else 1
-    with _disable_current_modes():
+    if True:
         args = tuple(torch.empty(tm if c[0] else 1, tn if c[1] else 1, device="meta") for c in classes)
         counts: List[int] = []
 

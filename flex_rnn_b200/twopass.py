@@ -30,7 +30,7 @@ from . import lower
 from .graph import MN, M1, N1, S11, StepGraph
 from .lower import (DT_BF16, DT_F16, DT_F32, DT_F64, GradOut, Problem, TensorSpec, choose_tile,
                     emit_backward, emit_forward)
-from .trace import as_tuple, trace_joint
+from .trace import as_tuple, run_isolated, trace_joint
 
 _DT = {th.float32: DT_F32, th.bfloat16: DT_BF16, th.float16: DT_F16, th.float64: DT_F64}
 _IO_DTYPES = (th.float32, th.bfloat16, th.float16, th.float64)
@@ -160,17 +160,22 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     nin, nst = len(inputs), len(state)
 
     # output arity and dtypes: run the step on meta tensors of the original dtypes
-    with th.utils._python_dispatch._disable_current_modes():
-        metas = [th.empty(B, H, *x.shape[-2:], dtype=x.dtype, device="meta") for x in inputs] + \
-                [th.empty(x.shape, dtype=x.dtype, device="meta") for x in state]
-        y_t, s_t = step(*metas)
-        y_t, s_t = as_tuple(y_t), as_tuple(s_t)
+    in_desc = [(tuple(x.shape[-2:]), x.dtype) for x in inputs]
+    st_desc = [(tuple(x.shape), x.dtype) for x in state]
+
+    def probe_step():
+        metas = [th.empty(B, H, *s, dtype=d, device="meta") for s, d in in_desc] + \
+                [th.empty(s, dtype=d, device="meta") for s, d in st_desc]
+        y, s = step(*metas)
+        return ([(tuple(o.shape), o.dtype) for o in as_tuple(y)], [(tuple(o.shape), o.dtype) for o in as_tuple(s)])
+
+    y_t, s_t = run_isolated(probe_step)
     assert len(s_t) == nst, f"step returns {len(s_t)} states but was given {nst}"
-    assert all(tuple(a.shape) == (B, H, M, N) for a in s_t), "new states must have the shape of the states"
-    assert all(list(o.shape) == [B, H, M, 1] for o in y_t), [tuple(o.shape) for o in y_t]
-    assert all(o.dtype in _IO_DTYPES for o in y_t)
+    assert all(a[0] == (B, H, M, N) for a in s_t), "new states must have the shape of the states"
+    assert all(list(o[0]) == [B, H, M, 1] for o in y_t), [o[0] for o in y_t]
+    assert all(o[1] in _IO_DTYPES for o in y_t)
     nout = len(y_t)
-    out_dtypes = [o.dtype for o in y_t]
+    out_dtypes = [o[1] for o in y_t]
 
     in_cls = [(int(x.shape[3] > 1), int(x.shape[4] > 1)) for x in inputs]
     st_cls = (int(M > 1), int(N > 1))

@@ -1,0 +1,149 @@
+"""Tracing, graph slicing, planner metadata and the front-end wiring (CPU only)."""
+import pytest
+import torch
+
+import flex_rnn_b200
+from flex_rnn_b200 import workloads as W
+from flex_rnn_b200.graph import MN, M1, N1, S11, UnsupportedStepOp
+from flex_rnn_b200.lower import LoweringError, choose_tile
+from flex_rnn_b200.trace import trace_joint
+from flex_rnn_b200.twopass import build_twopass, generate, make_plan, split_list, verify_meta
+
+
+def metas(op, B, T, H, M, N, dtype=torch.bfloat16):
+    xs, _, _ = W.synthetic(op, 2, 2, H, 4, 8, dtype)
+    ins = []
+    for x in xs[:-1]:
+        shape = [B if x.shape[0] > 1 else 1, T if x.shape[1] > 1 else 1, H, M if x.shape[3] > 1 else 1, N if x.shape[4] > 1 else 1]
+        ins.append(torch.empty(shape, dtype=dtype, device="meta"))
+    return tuple(ins), (torch.empty(B, H, M, N, dtype=dtype, device="meta"),)
+
+
+# per-element op counts of the joint graph ([M,N]-sized ops and sums of [M,N] operands)
+@pytest.mark.parametrize("op,k_fwd,k_joint", [("delta_rule", 6, 18), ("gated_delta_rule", 7, 22), ("rwkv7", 9, 28),
+                                              ("mamba2", 5, 16)])
+def test_op_counts_and_slices(op, k_fwd, k_joint):
+    ins, st = metas(op, 2, 16, 2, 32, 32)
+    plan, fw_meta, bw_meta = make_plan(W.STEPS[op], ins, st)
+    assert plan.k_fwd == k_fwd and plan.k_joint == k_joint
+    # the re-step is reduction free, the forward has only sums over n, aux are row sums
+    assert all(n.op != "sum" for n in plan.g_re.nodes)
+    assert all(not n.over_m for n in plan.g_fw.nodes if n.op == "sum")
+    assert len(plan.aux) == (0 if op == "mamba2" else 1)
+    assert all(plan.joint.shape[a] == M1 for a in plan.aux)
+    # declared metadata: y [B,T,H,M] in the step's dtype, states like S0, fp32 checkpoints and aux
+    assert tuple(fw_meta[0][0]) == (2, 16, 2, 32) and fw_meta[0][2] == torch.bfloat16
+    assert tuple(fw_meta[1][0]) == (2, 2, 32, 32)
+    assert fw_meta[2][2] == torch.float32 and tuple(fw_meta[2][0]) == (2, 2, plan.nck, 32, 32)
+    assert tuple(fw_meta[3][0]) == (len(plan.aux), 2, 2, 16, 32)
+    assert [tuple(m[0]) for m in bw_meta[:-1]] == [tuple(i.shape) for i in ins]
+
+
+def test_shape_classes():
+    g, no, ns = trace_joint(W.mamba2, [M1, S11, S11, N1, N1, MN], 5)
+    assert (no, ns) == (1, 1)
+    assert [g.shape[i] for i in g.inputs[:6]] == [M1, S11, S11, N1, N1, MN]
+    sums = [n for n in g.nodes if n.op == "sum"]
+    assert any(n.over_m and n.over_n for n in sums)          # d(dt*A) sums over the whole tile
+    assert any(n.over_m and not n.over_n for n in sums) and any(n.over_n and not n.over_m for n in sums)
+
+
+def test_state_with_one_column():
+    def hgrn(x, g, s):
+        s = g.exp() * s + x
+        return s, s
+    B, T, H, M = 2, 8, 1, 64
+    ins = (torch.empty(B, T, H, M, 1, device="meta"), torch.empty(B, T, H, M, 1, device="meta"))
+    plan, fw_meta, _ = make_plan(hgrn, ins, (torch.empty(B, H, M, 1, device="meta"),))
+    assert plan.problem.N == 1 and plan.aux == []
+    fw, bw = generate(plan)
+    assert "frnn_fw" in fw.source and "frnn_bw" in bw.source
+
+
+def test_input_validation_messages():
+    ins, st = metas("delta_rule", 2, 8, 2, 32, 32)
+    bad = list(ins)
+    bad[0] = torch.empty(2, 8, 2, 32, 32, dtype=torch.bfloat16, device="meta")
+    with pytest.raises(AssertionError, match="both a matrix for each head, and depends on time"):
+        make_plan(W.delta_rule, tuple(bad), st)
+    with pytest.raises(AssertionError, match="incompatible"):
+        make_plan(W.delta_rule, (torch.empty(2, 8, 2, 1, 7, device="meta"),) + ins[1:], st)
+    with pytest.raises(AssertionError, match="invalid shape"):
+        make_plan(W.delta_rule, (torch.empty(2, 8, 2, 32, device="meta"),) + ins[1:], st)
+    with pytest.raises(AssertionError, match="!="):
+        make_plan(W.delta_rule, ins, (torch.empty(2, 2, 32, 16, device="meta"),))
+
+    def col_sum(q, S):
+        S = S + q * S.sum(-2, True)
+        return (S * q).sum(-1, True), S
+    with pytest.raises(AssertionError, match="Only torch.sum"):
+        make_plan(col_sum, (ins[0],), st)
+
+    def unsupported(q, S):
+        S = S + torch.cumsum(q, -1)
+        return (S * q).sum(-1, True), S
+    with pytest.raises(UnsupportedStepOp):
+        make_plan(unsupported, (ins[0],), st)
+
+
+def test_cpu_tensors_are_rejected_not_emulated():
+    xs, _, _ = W.synthetic("delta_rule", 1, 4, 1, 32, 32, torch.float32)
+    with pytest.raises(RuntimeError, match="CUDA devices only"):
+        build_twopass(W.delta_rule, tuple(xs[:-1]), (xs[-1],))
+    op = flex_rnn_b200.jit(W.delta_rule)
+    with pytest.raises(RuntimeError, match="CUDA devices only"):
+        op(*xs)
+
+
+def test_dryrun_under_fake_mode():
+    """What torch.compile does: the fake implementation asks for output
+    metadata while a FakeTensorMode is active; nothing may touch CUDA."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    op = flex_rnn_b200.jit(W.rwkv7)
+    assert (op.ninputs, op.nstates, op.noutputs) == (6, 1, 1)
+    with FakeTensorMode():
+        B, T, H, M, N = 2, 16, 2, 32, 32
+        xs = [torch.empty(B, T, H, 1, N, dtype=torch.bfloat16) for _ in range(3)] + \
+             [torch.empty(B, T, H, M, 1, dtype=torch.bfloat16)] + \
+             [torch.empty(B, T, H, 1, N, dtype=torch.bfloat16) for _ in range(2)]
+        xs = [xs[0], xs[1], xs[2], xs[3], xs[4], xs[5]]
+        S0 = torch.empty(B, H, N, M, dtype=torch.bfloat16).mT
+        y, ST = op(*xs, S0)
+        assert y.shape == (B, T, H, M) and y.dtype == torch.bfloat16
+        assert ST.shape == (B, H, M, N) and ST.stride() == S0.stride()
+
+
+def test_naive_matches_simplified_naive():
+    xs, _, _ = W.synthetic("gated_delta_rule", 2, 6, 2, 8, 8, torch.float32)
+    op = flex_rnn_b200.jit(W.gated_delta_rule)
+    y, ST = op.naive(*xs)
+    y2, ST2 = flex_rnn_b200.simplified_naive(W.gated_delta_rule, *xs)
+    assert torch.allclose(y, y2) and torch.allclose(ST, ST2)
+    y64, _ = op.naive_fp64(*xs)
+    assert y64.dtype == torch.float64 and torch.allclose(y64.float(), y, atol=1e-5)
+    # the tests of the reference swap .apply for the naive callable; keep that working
+    op.apply = op.naive_fp64
+    assert op(*xs)[0].dtype == torch.float64
+
+
+def test_helpers():
+    assert split_list([1, 2, 3, 4], [1, 3]) == [[1], [2, 3, 4]]
+    with pytest.raises(AssertionError):
+        split_list([1, 2, 3], [1, 1])
+    a = torch.empty(2, 1, 3)
+    verify_meta([a], [torch.empty_strided((2, 1, 3), (3, 99, 1))])      # stride of a size-1 dim is ignored
+    with pytest.raises(AssertionError):
+        verify_meta([a], [torch.empty(2, 1, 3, dtype=torch.float64)])
+    with pytest.raises(AssertionError):
+        verify_meta([a], [torch.empty(3, 1, 2).transpose(0, 2)])
+
+
+def test_tile_chooser():
+    t = choose_tile(128, 128, 8, 8)
+    assert (t.R, t.C, t.L, t.G, t.NT, t.RG) == (8, 8, 16, 2, 256, 16)
+    t = choose_tile(128, 128, 4, 16, 32)
+    assert (t.MB, t.NT) == (32, 64)
+    t = choose_tile(64, 1, 4, 8)
+    assert t.C == 1 and t.L == 1 and t.NT % 32 == 0
+    with pytest.raises(LoweringError):
+        choose_tile(4, 4, 1, 1)
