@@ -199,6 +199,63 @@ def _pick_cnt(maxcnt: int, dt: int, *aligns: int) -> int:
 # graph body emission
 # ---------------------------------------------------------------------------
 
+def op_expr(n: Node, a: List[str]) -> str:
+    """C expression of one elementwise node given its operand expressions."""
+    op = n.op
+    if op == "mul":
+        return f"{a[0]} * {a[1]}"
+    if op == "add":
+        return f"{a[0]} + {a[1]}"
+    if op == "sub":
+        return f"{a[0]} - {a[1]}"
+    if op == "div":
+        return f"frnn_divf({a[0]}, {a[1]})"
+    if op == "neg":
+        return f"-{a[0]}"
+    if op in ("copy", "const"):
+        return a[0]
+    if op == "exp":
+        return f"frnn_expf({a[0]})"
+    if op == "log":
+        return f"frnn_logf({a[0]})"
+    if op == "sqrt":
+        return f"frnn_sqrtf({a[0]})"
+    if op == "rsqrt":
+        return f"frnn_rcpf(frnn_sqrtf({a[0]}))"
+    if op == "reciprocal":
+        return f"frnn_rcpf({a[0]})"
+    if op == "abs":
+        return f"fabsf({a[0]})"
+    if op == "sigmoid":
+        return f"frnn_rcpf(1.0f + frnn_expf(-{a[0]}))"
+    if op == "tanh":
+        return f"(1.0f - 2.0f * frnn_rcpf(1.0f + frnn_expf(2.0f * {a[0]})))"
+    if op == "log1p":
+        return f"frnn_logf(1.0f + {a[0]})"
+    if op == "expm1":
+        return f"(frnn_expf({a[0]}) - 1.0f)"
+    if op == "relu":
+        return f"fmaxf({a[0]}, 0.0f)"
+    if op == "sign":
+        return f"(({a[0]} > 0.0f) ? 1.0f : (({a[0]} < 0.0f) ? -1.0f : 0.0f))"
+    if op in ("gt", "lt", "ge", "le", "eq", "ne"):
+        sym = {"gt": ">", "lt": "<", "ge": ">=", "le": "<=", "eq": "==", "ne": "!="}[op]
+        return f"(({a[0]} {sym} {a[1]}) ? 1.0f : 0.0f)"
+    if op == "maximum":
+        return f"fmaxf({a[0]}, {a[1]})"
+    if op == "minimum":
+        return f"fminf({a[0]}, {a[1]})"
+    if op == "pow":
+        if not isinstance(n.args[1], str) and float(n.args[1]) == 2.0:
+            return f"{a[0]} * {a[0]}"
+        if not isinstance(n.args[1], str) and float(n.args[1]) == 3.0:
+            return f"{a[0]} * {a[0]} * {a[0]}"
+        return f"powf({a[0]}, {a[1]})"
+    if op == "where":
+        return f"(({a[0]} != 0.0f) ? {a[1]} : {a[2]})"
+    raise LoweringError(f"no lowering for op {op}")
+
+
 class Body:
     """Emits per-thread code for graph nodes over R x C register tiles."""
 
@@ -207,13 +264,14 @@ class Body:
         self.t = tile
         self.shape = dict(shapes)
         self.partial: Dict[str, bool] = {}     # value is a per-row-group partial sum
+        self.alias: Dict[str, str] = {}        # value name -> name of the register tile that holds it
 
     # element accessor of a value (or literal) at tile position (r, c)
     def at(self, a, r: str, c: str) -> str:
         if not isinstance(a, str):
             return flit(a)
         s = self.shape[a]
-        n = vname(a)
+        n = vname(self.alias.get(a, a))
         if s == MN:
             return f"{n}[{r}*{self.t.C}+{c}]"
         if s == M1:
@@ -225,11 +283,9 @@ class Body:
     def size(self, s: Shape) -> int:
         return (self.t.R if s[0] else 1) * (self.t.C if s[1] else 1)
 
-    def declare(self, name: str, s: Shape, init: Optional[str] = None):
+    def declare(self, name: str, s: Shape):
         self.shape[name] = s
         self.w(f"float {vname(name)}[{self.size(s)}];")
-        if init is not None:
-            self.loops(s, lambda r, c: f"{self.at(name, r, c)} = {init};")
 
     def loops(self, s: Shape, body):
         w = self.w
@@ -244,64 +300,6 @@ class Body:
             w.close()
         if s[0]:
             w.close()
-
-    def expr(self, n: Node, r: str, c: str) -> str:
-        a = [self.at(x, r, c) for x in n.args]
-        op = n.op
-        if op == "mul":
-            return f"{a[0]} * {a[1]}"
-        if op == "add":
-            return f"{a[0]} + {a[1]}"
-        if op == "sub":
-            return f"{a[0]} - {a[1]}"
-        if op == "div":
-            return f"frnn_divf({a[0]}, {a[1]})"
-        if op == "neg":
-            return f"-{a[0]}"
-        if op == "copy":
-            return a[0]
-        if op == "const":
-            return a[0]
-        if op == "exp":
-            return f"frnn_expf({a[0]})"
-        if op == "log":
-            return f"frnn_logf({a[0]})"
-        if op == "sqrt":
-            return f"frnn_sqrtf({a[0]})"
-        if op == "rsqrt":
-            return f"frnn_rcpf(frnn_sqrtf({a[0]}))"
-        if op == "reciprocal":
-            return f"frnn_rcpf({a[0]})"
-        if op == "abs":
-            return f"fabsf({a[0]})"
-        if op == "sigmoid":
-            return f"frnn_rcpf(1.0f + frnn_expf(-{a[0]}))"
-        if op == "tanh":
-            return f"(1.0f - 2.0f * frnn_rcpf(1.0f + frnn_expf(2.0f * {a[0]})))"
-        if op == "log1p":
-            return f"frnn_logf(1.0f + {a[0]})"
-        if op == "expm1":
-            return f"(frnn_expf({a[0]}) - 1.0f)"
-        if op == "relu":
-            return f"fmaxf({a[0]}, 0.0f)"
-        if op == "sign":
-            return f"(({a[0]} > 0.0f) ? 1.0f : (({a[0]} < 0.0f) ? -1.0f : 0.0f))"
-        if op in ("gt", "lt", "ge", "le", "eq", "ne"):
-            sym = {"gt": ">", "lt": "<", "ge": ">=", "le": "<=", "eq": "==", "ne": "!="}[op]
-            return f"(({a[0]} {sym} {a[1]}) ? 1.0f : 0.0f)"
-        if op == "maximum":
-            return f"fmaxf({a[0]}, {a[1]})"
-        if op == "minimum":
-            return f"fminf({a[0]}, {a[1]})"
-        if op == "pow":
-            if not isinstance(n.args[1], str) and float(n.args[1]) == 2.0:
-                return f"{a[0]} * {a[0]}"
-            if not isinstance(n.args[1], str) and float(n.args[1]) == 3.0:
-                return f"{a[0]} * {a[0]} * {a[0]}"
-            return f"powf({a[0]}, {a[1]})"
-        if op == "where":
-            return f"(({a[0]} != 0.0f) ? {a[1]} : {a[2]})"
-        raise LoweringError(f"no lowering for op {op}")
 
     def _check_partial(self, n: Node) -> bool:
         """Propagate the 'partial over row groups' property; only operations
@@ -343,38 +341,67 @@ class Body:
             self.declare(n.name, n.shape)
             rs = "r" if n.shape[0] else "0"
             cs = "c" if n.shape[1] else "0"
-            # outer loops over the kept dims, inner accumulation over the reduced dims
+            # independent accumulators for every kept element, filled with the reduced
+            # index outermost so that consecutive FMAs belong to different chains
+            red_r = n.over_m and ss[0]
+            red_c = n.over_n and ss[1]
+            kept = self.size(n.shape)
+            chain = (t.R if red_r else 1) * (t.C if red_c else 1)
+            nacc = max(1, min(4, chain // 4))
+            while kept * nacc > 32 and nacc > 1:
+                nacc //= 2
             w.open("")
+            w(f"float acc[{kept * nacc}];")
+            w("#pragma unroll")
+            w(f"for (int q = 0; q < {kept * nacc}; q++) acc[q] = 0.0f;")
+            # loop nest: reduced dims outside, kept dims inside
+            opened = 0
+            if red_r:
+                w("#pragma unroll")
+                w.open(f"for (int r = 0; r < {t.R}; r++)")
+                opened += 1
+            if red_c:
+                w("#pragma unroll")
+                w.open(f"for (int c = 0; c < {t.C}; c++)")
+                opened += 1
             if n.shape[0]:
                 w("#pragma unroll")
                 w.open(f"for (int r = 0; r < {t.R}; r++)")
+                opened += 1
             if n.shape[1]:
                 w("#pragma unroll")
                 w.open(f"for (int c = 0; c < {t.C}; c++)")
-            w("float acc = 0.0f;")
-            if n.over_m and ss[0]:
-                w("#pragma unroll")
-                w.open(f"for (int r = 0; r < {t.R}; r++)")
-            if n.over_n and ss[1]:
-                w("#pragma unroll")
-                w.open(f"for (int c = 0; c < {t.C}; c++)")
-            w(f"acc += {self.at(src, 'r', 'c')};")
-            if n.over_n and ss[1]:
+                opened += 1
+            kidx = "0"
+            if n.shape == M1:
+                kidx = "r"
+            elif n.shape == N1:
+                kidx = "c"
+            ridx = "c" if red_c else "r"
+            if red_r and red_c:
+                ridx = f"(r * {t.C} + c)"
+            w(f"acc[({kidx}) * {nacc} + ({ridx}) % {nacc}] += {self.at(src, 'r', 'c')};")
+            for _ in range(opened):
                 w.close()
-            if n.over_m and ss[0]:
-                w.close()
-            if n.over_n and ss[1] and t.L > 1:
-                w(f"acc = frnn_row_sum<{t.L}>(acc);")
-            w(f"{self.at(n.name, rs, cs)} = acc;")
-            if n.shape[1]:
-                w.close()
-            if n.shape[0]:
-                w.close()
+            # totals, then (for sums over n) the butterflies of all kept elements together
+            w("#pragma unroll")
+            w.open(f"for (int k = 0; k < {kept}; k++)")
+            tot = " + ".join(f"acc[k * {nacc} + {q}]" for q in range(nacc))
+            if nacc == 4:
+                tot = f"(acc[k * 4] + acc[k * 4 + 1]) + (acc[k * 4 + 2] + acc[k * 4 + 3])"
+            w(f"{vname(n.name)}[k] = {tot};")
+            w.close()
+            if red_c and t.L > 1:
+                off = t.L // 2
+                while off > 0:
+                    w("#pragma unroll")
+                    w(f"for (int k = 0; k < {kept}; k++) {vname(n.name)}[k] += frnn_shfl_xor({vname(n.name)}[k], {off});")
+                    off //= 2
             w.close()
             return
         self.partial[n.name] = self._check_partial(n)
         self.declare(n.name, n.shape)
-        self.loops(n.shape, lambda r, c: f"{self.at(n.name, r, c)} = {self.expr(n, r, c)};")
+        self.loops(n.shape, lambda r, c: f"{self.at(n.name, r, c)} = {op_expr(n, [self.at(x, r, c) for x in n.args])};")
 
     def graph(self, g: StepGraph, allow_over_m: bool = False):
         for n in g.nodes:
@@ -413,8 +440,35 @@ def _elem_off(spec: TensorSpec, dims: Sequence[Tuple[int, str]]) -> str:
     return " + ".join(terms) if terms else "0L"
 
 
+def _contig(shape: Sequence[int]) -> Tuple[int, ...]:
+    st, acc = [], 1
+    for s in reversed(shape):
+        st.append(acc)
+        acc *= s
+    return tuple(reversed(st))
+
+
+def _merge_nodes(graphs: Sequence[StepGraph]) -> List[Node]:
+    seen, out = set(), []
+    for g in graphs:
+        for n in g.nodes:
+            if n.name not in seen:
+                seen.add(n.name)
+                out.append(n)
+    return out
+
+
 class KernelBuilder:
-    """State shared by the forward and backward emitters."""
+    """Staging machinery shared by the forward and backward emitters:
+
+    raw ring   two buffers of D timesteps of every per-timestep vector in its
+               I/O dtype, filled by TMA bulk copies (or plain loads);
+    work buf   one buffer of D timesteps in fp32 holding what the scan loop
+               actually reads: converted inputs plus every value of the step
+               graph that depends on inputs only and is not a full tile
+               ("hoisted": e.g. beta*k, v - aux, exp(dt*A)), computed once per
+               CTA by all threads when a raw chunk has arrived.
+    """
 
     def __init__(self, p: Problem, tile: Tile, dstage: int, use_tma: bool):
         self.p = p
@@ -425,6 +479,7 @@ class KernelBuilder:
         self.items: List[StagedItem] = []
         self.params: List[str] = []
         self.param_decl: List[str] = []
+        self.const_scalars: Dict[str, str] = {}    # time-invariant [1,1] inputs kept in registers
 
     # -- parameters ----------------------------------------------------------
     def add_param(self, name: str, ctype: str, const: bool):
@@ -433,7 +488,7 @@ class KernelBuilder:
         r = " __restrict__" if const else ""
         self.param_decl.append(f"{q}{ctype}*{r} {name}")
 
-    # -- staging plan ----------------------------------------------------------
+    # -- raw staging plan ------------------------------------------------------
     def add_item(self, key: str, cls: Shape, spec: TensorSpec, ptr: str, dims: Dict[str, int]):
         """``dims`` maps 'b','t','h','v' (the vector dim) to tensor dim indices."""
         t = self.t
@@ -445,23 +500,60 @@ class KernelBuilder:
         base = _elem_off(spec, base_dims)
         e = ELT[spec.dt]
         st_t = spec.st(dims["t"])
-        tma = (self.use_tma and cls != S11 and inner == 1 and spec.aligned16
+        tma = (self.use_tma and cls != S11 and (inner == 1 or length == 1) and spec.aligned16
                and (length * e) % 16 == 0 and (st_t * e) % 16 == 0
                and (spec.st(dims["b"]) * e) % 16 == 0 and (spec.st(dims["h"]) * e) % 16 == 0
                and (cls != M1 or (t.MB * spec.st(dims["v"]) * e) % 16 == 0))
         rowb = (length * e + 15) // 16 * 16
         self.items.append(StagedItem(key, cls, spec.dt, ptr, length, base, st_t, inner, tma, 0, rowb))
 
-    def layout_stage(self) -> int:
+    def plan(self, graphs: Sequence[StepGraph], outputs_needed: Sequence[str] = ()) -> List[StepGraph]:
+        """Lay out the raw ring, decide what is hoisted into the work buffer and
+        return the graphs rewritten to read those values as inputs."""
         off = 0
-        # TMA items first (16-byte aligned rows), then plain ones
         for it in sorted(self.items, key=lambda i: not i.tma):
             it.off = off
             off += it.rowb * self.D
         self.stage_bytes = (off + 127) // 128 * 128
         self.tma_items = [i for i in self.items if i.tma]
         self.plain_items = [i for i in self.items if not i.tma]
-        return self.stage_bytes
+        self.item_by_key = {i.key: i for i in self.items}
+
+        avail: Dict[str, Shape] = {i.key: i.cls for i in self.items}
+        for nm in self.const_scalars:
+            avail[nm] = S11
+        self.hoisted: List[Node] = []
+        for n in _merge_nodes(graphs):
+            if n.op == "sum" or n.shape == MN or n.name in avail:
+                continue
+            if all(a in avail for a in n.value_args()):
+                avail[n.name] = n.shape
+                self.hoisted.append(n)
+        hoisted_names = {n.name for n in self.hoisted}
+        used_outside = set(outputs_needed)
+        for g in graphs:
+            for n in g.nodes:
+                if n.name not in hoisted_names:
+                    used_outside.update(n.value_args())
+            used_outside.update(g.outputs)
+        frontier = [nm for nm in avail if nm in used_outside and nm not in self.const_scalars]
+        # work-buffer layout: per timestep all 1N values, then M1, then scalars
+        self.wk: Dict[str, Tuple[Shape, int]] = {}
+        pos = 0
+        for cls, ln in ((N1, self.p.N), (M1, self.t.MB), (S11, 1)):
+            pos = (pos + 3) // 4 * 4
+            for nm in frontier:
+                if avail[nm] == cls:
+                    self.wk[nm] = (cls, pos)
+                    pos += ln
+        self.wk_row = (pos + 3) // 4 * 4
+        self.wk_bytes = (self.wk_row * 4 * self.D + 127) // 128 * 128 if self.wk else 0
+        self.avail = avail
+        out = []
+        for g in graphs:
+            g2 = g.pruned(g.outputs, g.name, leaves=[nm for nm in frontier if nm not in g.inputs])
+            out.append(g2)
+        return out
 
     # -- code pieces -------------------------------------------------------------
     def emit_thread_ids(self):
@@ -472,7 +564,7 @@ class KernelBuilder:
         w(f"const int m0 = blockIdx.x * {t.MB}, h = blockIdx.y, b = blockIdx.z;")
         w(f"const int row0 = m0 + rg * {t.R};  // first state row of this thread")
         w(f"const int cb = {t.V} * l;          // first state column of this thread")
-        w("(void)row0; (void)cb; (void)m0; (void)h; (void)b;")
+        w("(void)row0; (void)cb; (void)m0; (void)h; (void)b; (void)warp;")
 
     def emit_tma_issue(self, fn: str):
         """Device function issuing the bulk copies of one chunk (warp 0 calls)."""
@@ -480,8 +572,9 @@ class KernelBuilder:
         n = len(self.tma_items)
         bytes_per_step = sum(i.length * ELT[i.dt] for i in self.tma_items)
         w(f"// bulk copies of one chunk: {n} vectors per timestep, {bytes_per_step} bytes per timestep")
-        self.tma_issue_args = ", ".join(f"const void* {i.ptr}" for i in self._uniq_ptr_items(self.tma_items))
-        self.tma_issue_call = ", ".join(i.ptr for i in self._uniq_ptr_items(self.tma_items))
+        uniq = self._uniq_ptr_items(self.tma_items)
+        self.tma_issue_args = ", ".join(f"const void* {i.ptr}" for i in uniq)
+        self.tma_issue_call = ", ".join(i.ptr for i in uniq)
         w.open(f"FRNN_DEV void {fn}(unsigned char* stage, u64* bar, int t0, int nv, int lane, int b, int h, int m0"
                + (", " + self.tma_issue_args if n else "") + ")")
         if n:
@@ -538,23 +631,83 @@ class KernelBuilder:
             w(f"if (tl < {self.D}) (({CTYPE[it.dt]}*)({stage} + {it.off} + tl * {it.rowb}))[j] = pl{k}[q];")
             w.close()
 
-    def emit_item_read(self, body: Body, it: StagedItem, sp: str, name: str):
-        """Read one staged vector of the current timestep into registers."""
+    def emit_convert(self, raw: str, wk: str, nv: str):
+        """All threads: raw chunk -> fp32 work buffer, evaluating hoisted nodes."""
         w, t = self.w, self.t
-        body.declare(name, it.cls)
+        hoisted = {n.name: n for n in self.hoisted}
+
+        def closure(targets: List[str]) -> List[str]:
+            need, order = set(), []
+
+            def visit(nm):
+                if nm in need:
+                    return
+                need.add(nm)
+                if nm in hoisted:
+                    for a in hoisted[nm].value_args():
+                        visit(a)
+                order.append(nm)
+            for tg in targets:
+                visit(tg)
+            return order
+
+        for cls, ln in ((N1, self.p.N), (M1, t.MB), (S11, 1)):
+            targets = [nm for nm, (c, _) in self.wk.items() if c == cls]
+            if not targets:
+                continue
+            order = closure(targets)
+            vw = 4 if ln % 4 == 0 else (2 if ln % 2 == 0 else 1)   # elements per thread and iteration
+            w.open(f"for (int e = tid; e < {nv} * {ln // vw}; e += {t.NT})")
+            w(f"const int tl = e / {ln // vw}, i = (e % {ln // vw}) * {vw}; (void)i;")
+            for nm in order:
+                hn = "h_" + nm.replace(".", "_")
+                if nm in hoisted:
+                    n = hoisted[nm]
+                    width = vw if n.shape != S11 else 1
+                    w(f"float {hn}[{width}];")
+                    for q in range(width):
+                        ops = []
+                        for a in n.args:
+                            if not isinstance(a, str):
+                                ops.append(flit(a))
+                            else:
+                                aw = vw if self.avail[a] != S11 else 1
+                                ops.append(f"h_{a.replace('.', '_')}[{q if aw > 1 else 0}]")
+                        w(f"{hn}[{q}] = {op_expr(n, ops)};")
+                elif nm in self.const_scalars:
+                    w(f"float {hn}[1]; {hn}[0] = {self.const_scalars[nm]};")
+                else:
+                    it = self.item_by_key[nm]
+                    if it.cls == S11:
+                        w(f"float {hn}[1]; {hn}[0] = frnn_io<{it.dt}>::ld({raw} + {it.off} + tl * {it.rowb}, 0);")
+                    else:
+                        w(f"float {hn}[{vw}]; frnn_ldv<{it.dt},{vw}>({raw} + {it.off} + tl * {it.rowb}, i, {hn});")
+            for nm in targets:
+                hn = "h_" + nm.replace(".", "_")
+                if cls == S11:
+                    w(f"{wk}[tl * {self.wk_row} + {self.wk[nm][1]}] = {hn}[0];")
+                else:
+                    w(f"frnn_stv<0,{vw}>({wk}, tl * {self.wk_row} + {self.wk[nm][1]} + i, {hn});")
+            w.close()
+
+    def emit_wk_read(self, body: Body, name: str, wkt: str):
+        """Read one work-buffer value of the current timestep into registers.
+        ``wkt`` points at the timestep's row of the work buffer."""
+        w, t = self.w, self.t
+        cls, off = self.wk[name]
+        body.declare(name, cls)
         n = vname(name)
-        src = f"({sp} + {it.off} + tl * {it.rowb})"
-        if it.cls == N1:
-            cnt = _pick_cnt(t.V, it.dt)
+        if cls == N1:
+            cnt = _pick_cnt(t.V, DT_F32)
             for j in range(t.NCH):
                 for q in range(t.V // cnt):
-                    w(f"frnn_ldv<{it.dt},{cnt}>({src}, cb + {j * t.V * t.L + q * cnt}, &{n}[{j * t.V + q * cnt}]);")
-        elif it.cls == M1:
-            cnt = _pick_cnt(t.R, it.dt, t.R)
+                    w(f"frnn_ldv<0,{cnt}>({wkt}, {off} + cb + {j * t.V * t.L + q * cnt}, &{n}[{j * t.V + q * cnt}]);")
+        elif cls == M1:
+            cnt = _pick_cnt(t.R, DT_F32, t.R)
             for q in range(t.R // cnt):
-                w(f"frnn_ldv<{it.dt},{cnt}>({src}, rg * {t.R} + {q * cnt}, &{n}[{q * cnt}]);")
+                w(f"frnn_ldv<0,{cnt}>({wkt}, {off} + rg * {t.R} + {q * cnt}, &{n}[{q * cnt}]);")
         else:
-            w(f"{n}[0] = frnn_io<{it.dt}>::ld({src}, 0);")
+            w(f"{n}[0] = {wkt}[{off}];")
 
     def emit_const_input(self, body: Body, name: str, cls: Shape, spec: TensorSpec, ptr: str,
                          dims: Dict[str, int]):
@@ -566,28 +719,25 @@ class KernelBuilder:
         if cls == S11:
             w(f"{n}[0] = frnn_io<{spec.dt}>::ld({ptr}, {base});")
             return
-        if cls in (N1, MN):
-            ncol = dims["n"]
-        if cls in (M1, MN):
-            nrow = dims["m"]
         if cls == N1:
             for j in range(t.NCH):
                 for e in range(t.V):
-                    w(f"{n}[{j * t.V + e}] = frnn_io<{spec.dt}>::ld({ptr}, {base} + (long){t.col(j, e)} * {spec.st(ncol)}L);")
+                    w(f"{n}[{j * t.V + e}] = frnn_io<{spec.dt}>::ld({ptr}, {base} + (long){t.col(j, e)} * {spec.st(dims['n'])}L);")
         elif cls == M1:
             w("#pragma unroll")
             w.open(f"for (int r = 0; r < {t.R}; r++)")
-            w(f"{n}[r] = frnn_io<{spec.dt}>::ld({ptr}, {base} + (long)(row0 + r) * {spec.st(nrow)}L);")
+            w(f"{n}[r] = frnn_io<{spec.dt}>::ld({ptr}, {base} + (long)(row0 + r) * {spec.st(dims['m'])}L);")
             w.close()
         else:
-            self.emit_tile_global(n, spec, ptr, base, nrow, ncol, load=True)
+            self.emit_tile_global(n, spec, ptr, base, dims["m"], dims["n"], load=True)
 
     def emit_tile_global(self, arr: str, spec: TensorSpec, ptr: str, base: str, dm: int, dn: int,
                          load: bool, add: bool = False):
         """Strided global load / store of an R x C register tile (any strides)."""
         w, t = self.w, self.t
         sm, sn = spec.st(dm), spec.st(dn)
-        if sn == 1 and t.V > 1 and spec.aligned16 and (sm * ELT[spec.dt]) % 16 == 0 and not add:
+        if sn == 1 and t.V > 1 and spec.aligned16 and (sm * ELT[spec.dt]) % 16 == 0 and not add \
+                and all((s * ELT[spec.dt]) % 16 == 0 for s in spec.stride[:-1]):
             cnt = _pick_cnt(t.V, spec.dt)
             w("#pragma unroll")
             w.open(f"for (int r = 0; r < {t.R}; r++)")
@@ -647,16 +797,39 @@ def _header(src_prelude: str) -> str:
     return src_prelude.replace("#pragma once", "")
 
 
+def _stage_inputs(kb: KernelBuilder, p: Problem, used: Sequence[bool], allow_mn: bool) -> List[int]:
+    """Register the time-varying inputs as staged items; return the indices of
+    the time-invariant ones (loaded once into registers)."""
+    const_inputs = []
+    for i, spec in enumerate(p.inputs):
+        if not used[i]:
+            continue
+        cls = p.in_cls(i)
+        if cls == MN and spec.shape[1] != 1:
+            raise LoweringError("an input that is a full matrix per head must not depend on time")
+        if cls == MN and not allow_mn:
+            raise LoweringError("matrix-per-head inputs are not supported by the backward kernel yet")
+        if spec.shape[1] == 1:
+            const_inputs.append(i)
+            if cls == S11:
+                kb.const_scalars[p.in_names[i]] = f"{vname(p.in_names[i])}[0]"
+        else:
+            kb.add_item(p.in_names[i], cls, spec, f"in{i}", _in_dims(cls))
+    return const_inputs
+
+
 # ---------------------------------------------------------------------------
 # forward kernel
 # ---------------------------------------------------------------------------
 
 def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, tile: Tile,
                  dstage: int, dck: int, use_tma: bool, min_blocks: int, prelude: str,
-                 kname: str = "frnn_fw") -> KernelSource:
+                 kname: str = "frnn_fw", final_ckpt: bool = False, step_unroll: int = 2) -> KernelSource:
     """Forward scan.  ``g`` computes [*outputs, *new_states, *aux] from
     [*inputs, *states].  Kernel parameters, in order: used inputs, initial
-    states, outputs, final states, checkpoints, aux, error word."""
+    states, outputs, final states, checkpoints, aux, error word.  With
+    ``final_ckpt`` one more fp32 checkpoint (the final state) is stored at
+    index ceil(T/dck)."""
     kb = KernelBuilder(p, tile, dstage, use_tma)
     w, t = kb.w, tile
     ns = len(p.states)
@@ -677,22 +850,15 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     kb.add_param("aux", "float", False)
     kb.add_param("err", "int", False)
 
-    const_inputs = []
-    for i, spec in enumerate(p.inputs):
-        if not used[i]:
-            continue
-        cls = p.in_cls(i)
-        if cls == MN or spec.shape[1] == 1:
-            if cls == MN and spec.shape[1] != 1:
-                raise LoweringError("an input that is a full matrix per head must not depend on time")
-            const_inputs.append(i)
-        else:
-            kb.add_item(p.in_names[i], cls, spec, f"in{i}", _in_dims(cls))
-    stage_bytes = kb.layout_stage()
+    const_inputs = _stage_inputs(kb, p, used, allow_mn=True)
+    (g2,) = kb.plan([g])
+    stage_bytes = kb.stage_bytes
     BAR_BYTES = 128
-    smem_bytes = BAR_BYTES + 2 * stage_bytes
+    off_wk = BAR_BYTES + 2 * stage_bytes
+    smem_bytes = off_wk + kb.wk_bytes
     nchunk = (p.T + dstage - 1) // dstage
     nck = (p.T + dck - 1) // dck
+    nck_store = nck + (1 if final_ckpt else 0)
 
     w(_header(prelude))
     w(f"// forward scan: B={p.B} T={p.T} H={p.H} M={p.M} N={p.N}; tile R={t.R} C={t.C} L={t.L} MB={t.MB}; "
@@ -704,6 +870,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     kb.emit_thread_ids()
     w("u64* full = (u64*)smem;")
     w(f"unsigned char* stage = smem + {BAR_BYTES};")
+    w(f"float* wk = (float*)(smem + {off_wk});")
     has_tma = bool(kb.tma_items)
     if has_tma:
         w.open("if (tid == 0)")
@@ -721,10 +888,9 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         if nchunk > 1:
             w(f"fw_issue(stage + {stage_bytes}, &full[1], {dstage}, min({dstage}, {p.T - dstage}), lane, b, h, m0{tma_call});")
         w.close()
-    w("frnn_block_sync();")
 
-    body = Body(w, t, g.shape)
-    # states
+    body = Body(w, t, g2.shape)
+    ckspec = TensorSpec((p.B, p.H, nck_store, p.M, p.N), _contig((p.B, p.H, nck_store, p.M, p.N)), DT_F32)
     for k in range(ns):
         body.declare(p.st_names[k], stcls)
         kb.emit_tile_global(vname(p.st_names[k]), p.states[k], f"s0_{k}",
@@ -744,23 +910,39 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         w("}")
     if has_tma:
         w(f"if (!frnn_mbar_wait(&full[buf], (c >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+    w("frnn_block_sync();   // previous chunk's work buffer is no longer read; plain stores are visible")
+    kb.emit_convert("sp", "wk", "nv")
+    if kb.plain_items:
+        w(f"if (c + 1 < {nchunk}) {{")
+        w.ind += 1
+        kb.emit_plain_store(f"(stage + (buf ^ 1) * {stage_bytes})")
+        w.ind -= 1
+        w("}")
+    w("frnn_block_sync();   // work buffer complete; the raw buffer may be refilled")
+    if has_tma:
+        w.open(f"if (warp == 0 && c + 2 < {nchunk})")
+        w(f"fw_issue(sp, &full[buf], t0 + {2 * dstage}, min({dstage}, {p.T} - t0 - {2 * dstage}), lane, b, h, m0{tma_call});")
+        w.close()
+    sub_len = math.gcd(dstage, dck)
     w("#pragma unroll 1")
-    w.open("for (int tl = 0; tl < nv; tl++)")
-    w("const int t = t0 + tl;")
-    # checkpoint of the state before step t
-    w.open(f"if (t % {dck} == 0)")
+    w.open(f"for (int tl0 = 0; tl0 < nv; tl0 += {sub_len})")
+    w.open(f"if ((t0 + tl0) % {dck} == 0)")
     for k in range(ns):
-        ckspec = TensorSpec((p.B, p.H, nck, p.M, p.N), _contig((p.B, p.H, nck, p.M, p.N)), DT_F32)
-        base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, f"t / {dck}")])
+        base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, f"(t0 + tl0) / {dck}")])
         kb.emit_tile_global(vname(p.st_names[k]), ckspec, f"ck{k}", base, 3, 4, load=False)
     w.close()
+    w(f"const int tl1 = min(tl0 + {sub_len}, nv);")
+    w(f"#pragma unroll {step_unroll}")
+    w.open("for (int tl = tl0; tl < tl1; tl++)")
+    w("const int t = t0 + tl;")
+    w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
     sub = Body(w, t, body.shape)
     w.open("")
-    for it in kb.items:
-        kb.emit_item_read(sub, it, "sp", it.key)
-    sub.graph(g, allow_over_m=False)
-    outs = g.outputs
-    # outputs y_j -> out[b, t, h, m]
+    for nm in g2.inputs:
+        if nm in kb.wk and g2.used_inputs()[g2.inputs.index(nm)]:
+            kb.emit_wk_read(sub, nm, "wkt")
+    sub.graph(g2, allow_over_m=False)
+    outs = g2.outputs
     yspec_shape = (p.B, p.T, p.H, p.M)
     for j in range(n_out):
         o = outs[j]
@@ -771,7 +953,6 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         kb.emit_row_vec_store(f"yv{j}", p.out_dt[j], f"out{j}",
                               _elem_off(ys, [(0, "b"), (1, "t"), (2, "h")]), 1,
                               (p.M * ELT[p.out_dt[j]]) % 16 == 0)
-    # aux row sums -> aux[a, b, h, t, m]
     ashape = (max(1, p.naux), p.B, p.H, p.T, p.M)
     aspec = TensorSpec(ashape, _contig(ashape), DT_F32)
     for a, an in enumerate(aux_names):
@@ -781,40 +962,23 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         kb.emit_row_vec_store(f"av{a}", DT_F32, "aux",
                               _elem_off(aspec, [(0, str(a)), (1, "b"), (2, "h"), (3, "t")]), 1,
                               (p.M * 4) % 16 == 0)
-    # new state
     for k in range(ns):
         o = outs[n_out + k]
         sub.loops(stcls, lambda r, c, k=k, o=o: f"{body.at(p.st_names[k], r, c)} = {sub.at(o, r, c)};")
     w.close()
     w.close()  # tl loop
-    if kb.plain_items:
-        w(f"if (c + 1 < {nchunk}) {{")
-        w.ind += 1
-        kb.emit_plain_store(f"(stage + (buf ^ 1) * {stage_bytes})")
-        w.ind -= 1
-        w("}")
-    w("frnn_block_sync();")
-    if has_tma:
-        w.open(f"if (warp == 0 && c + 2 < {nchunk})")
-        w(f"fw_issue(sp, &full[buf], t0 + {2 * dstage}, min({dstage}, {p.T} - t0 - {2 * dstage}), lane, b, h, m0{tma_call});")
-        w.close()
+    w.close()  # tl0 loop
     w.close()  # chunk loop
     for k in range(ns):
-        # final state, laid out like the initial state
         kb.emit_tile_global(vname(p.st_names[k]), p.states[k], f"sT_{k}",
                             _elem_off(p.states[k], [(0, "b"), (1, "h")]), 2, 3, load=False)
+        if final_ckpt:
+            base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, str(nck))])
+            kb.emit_tile_global(vname(p.st_names[k]), ckspec, f"ck{k}", base, 3, 4, load=False)
     w.close()
     return KernelSource(kname, w.text(), (p.M // t.MB, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
-                        {"stage_bytes": stage_bytes, "tma_items": len(kb.tma_items),
-                         "plain_items": len(kb.plain_items), "nck": nck})
-
-
-def _contig(shape: Sequence[int]) -> Tuple[int, ...]:
-    st, acc = [], 1
-    for s in reversed(shape):
-        st.append(acc)
-        acc *= s
-    return tuple(reversed(st))
+                        {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "tma_items": len(kb.tma_items),
+                         "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted]})
 
 
 # ---------------------------------------------------------------------------
@@ -832,20 +996,41 @@ class GradOut:
     atomic: bool             # input broadcast over B, T or H: atomicAdd into fp32
 
 
+@dataclass
+class Reverse:
+    """Exact-up-to-rounding inverse of an additive re-step: S_t = S_{t+1} -/+ X_t."""
+    graph: StepGraph          # computes the increments [X_k] from inputs and aux
+    sign: List[int]           # +1 if S' = S + X, -1 if S' = S - X
+    resync: int               # chunks between reloads of an exact forward checkpoint
+
+
 def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[str], n_out: int,
-                  grads: List[GradOut], dstate_names: List[str], dy_names: List[str],
-                  dnext_names: List[str], tile: Tile, seg: int, nslots: int, use_tma: bool,
-                  prelude: str, kname: str = "frnn_bw", red_bufs: int = 2) -> KernelSource:
+                  grads: List[GradOut], dy_names: List[str], dnext_names: List[str], tile: Tile,
+                  seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
+                  kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
+                  step_unroll: int = 2) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
     ``g_bw`` computes [*d_inputs, *d_states] from
     [*inputs, *states, *d_outputs, *d_new_states, *aux].
-    Checkpoint chunk length D = seg * nslots.  Parameters, in order: used
-    inputs, d_outputs, d_final_states, checkpoints, aux, d_initial_states,
-    input gradients (those in ``grads``), error word.
+
+    Generic mode: a checkpoint chunk is D = seg * nslots steps; segment bases
+    are rebuilt forward into shared-memory slots and the states inside a
+    segment are recomputed from the base.  Reverse mode (additive re-steps
+    only): the state is stepped *backwards* with the saved row sums, no slots;
+    D = seg is the staging chunk and every ``reverse.resync`` chunks the state
+    is reloaded from an exact forward checkpoint (checkpoint interval
+    D * resync).
+
+    Per-column and per-head gradient partials of ``kflush`` consecutive steps
+    are collected in a shared ring and reduced over the row groups together.
+
+    Parameters, in order: used inputs, d_outputs, d_final_states,
+    checkpoints, aux, d_initial_states, input gradients, error word.
     """
-    D = seg * nslots
+    rev = reverse is not None
+    D = seg if rev else seg * nslots
     kb = KernelBuilder(p, tile, D, use_tma)
     w, t = kb.w, tile
     if t.MB != p.M:
@@ -853,10 +1038,26 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     ns = len(p.states)
     stcls = p.st_cls()
     nin = len(p.inputs)
-    used_re, used_bw = g_re.used_inputs(), g_bw.used_inputs()
-    used = [used_re[i] or used_bw[i] for i in range(nin)]
-    dy_used = [used_bw[nin + ns + j] for j in range(n_out)]
-    nck = (p.T + D - 1) // D
+    alias_next: List[str] = []
+    if rev:
+        # the post-step state is in registers before the reverse step: let the backward graph read it
+        # instead of recomputing it, provided no node needs both the post-step and the pre-step state
+        ns_names = list(g_re.outputs)
+        probe = g_bw.pruned(g_bw.outputs, g_bw.name, leaves=[n for n in ns_names if n not in g_bw.inputs])
+        dep_next = probe.depends_on(ns_names) - set(ns_names)
+        dep_cur = probe.depends_on(p.st_names)
+        if not (dep_next & dep_cur) and not (set(ns_names) & dep_cur) and all(n in probe.inputs for n in ns_names):
+            g_bw = probe
+            alias_next = ns_names
+    graphs = [g_bw] + ([reverse.graph] if rev else [g_re])
+    used_lists = [g.used_inputs() for g in graphs]
+    used = [any(u[i] for u in used_lists) for i in range(nin)]
+    used_bw0 = g_bw.used_inputs()
+    dy_used = [used_bw0[nin + ns + j] for j in range(n_out)]
+    nchunk = (p.T + D - 1) // D
+    dck = D * (reverse.resync if rev else 1)
+    nck = (p.T + dck - 1) // dck
+    nck_store = nck + (1 if rev else 0)
 
     for i in range(nin):
         if used[i]:
@@ -874,19 +1075,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         kb.add_param(f"dx{go.index}", "void", False)
     kb.add_param("err", "int", False)
 
-    const_inputs = []
-    for i, spec in enumerate(p.inputs):
-        if not used[i]:
-            continue
-        cls = p.in_cls(i)
-        if cls == MN:
-            raise LoweringError("matrix-per-head inputs are not supported by the backward kernel yet")
-        if spec.shape[1] == 1:
-            const_inputs.append(i)
-        else:
-            kb.add_item(p.in_names[i], cls, spec, f"in{i}", _in_dims(cls))
+    const_inputs = _stage_inputs(kb, p, used, allow_mn=False)
     ashape = (max(1, p.naux), p.B, p.H, p.T, p.M)
-    aspec = TensorSpec(ashape, _contig(ashape), DT_F32)
     for a, an in enumerate(aux_names):
         sp_a = TensorSpec(ashape[1:], _contig(ashape)[1:], DT_F32)
         kb.add_item(an, M1, sp_a, "aux", {"b": 0, "h": 1, "t": 2, "v": 3})
@@ -896,31 +1086,34 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if dy_used[j]:
             ys = TensorSpec(yshape, _contig(yshape), p.out_dt[j])
             kb.add_item(dy_names[j], M1, ys, f"dy{j}", {"b": 0, "t": 1, "h": 2, "v": 3})
-    stage_bytes = kb.layout_stage()
+    planned = kb.plan(graphs)
+    g_bw2, g_aux2 = planned[0], planned[1]
+    stage_bytes = kb.stage_bytes
 
-    # partial-sum exchange layout: per row group, all 1N gradients then all 11 gradients
+    # gradient-partial ring: per step and row group all 1N gradients, then all 11 gradients
     pm_vec = [go for go in grads if go.cls == N1]
     pm_sc = [go for go in grads if go.cls == S11]
+    vw = 4 if p.N % 4 == 0 else (2 if p.N % 2 == 0 else 1)
     redw = len(pm_vec) * p.N + len(pm_sc)
     redw_pad = (redw + 3) // 4 * 4
-    red_bytes = red_bufs * t.RG * redw_pad * 4 if redw else 0
-    nphys = max(nslots, 2)
+    step_floats = t.RG * redw_pad
+    ring_bytes = ring_bufs * kflush * step_floats * 4 if redw else 0
+    nphys = 0 if rev else max(nslots, 2)
     slot_elems = p.M * p.N
     slot_bytes = slot_elems * 4
-    ck_tma = use_tma and slot_bytes % 16 == 0
+    ck_tma = (not rev) and use_tma and slot_bytes % 16 == 0
     BAR_BYTES = 128
     off_stage = BAR_BYTES
-    off_slots = off_stage + 2 * stage_bytes
-    off_red = off_slots + nphys * ns * slot_bytes
-    smem_bytes = off_red + red_bytes
+    off_wk = off_stage + 2 * stage_bytes
+    off_slots = off_wk + kb.wk_bytes
+    off_ring = off_slots + nphys * ns * slot_bytes
+    smem_bytes = off_ring + ring_bytes
 
     w(_header(prelude))
-    w(f"// backward scan: B={p.B} T={p.T} H={p.H} M={p.M} N={p.N}; tile R={t.R} C={t.C} L={t.L}; "
-      f"chunk {D} = {nslots} segments x {seg} steps")
+    mode = f"reverse re-step, resync every {dck} steps" if rev else f"chunk {D} = {nslots} segments x {seg} steps"
+    w(f"// backward scan: B={p.B} T={p.T} H={p.H} M={p.M} N={p.N}; tile R={t.R} C={t.C} L={t.L}; {mode}; "
+      f"gradient partials flushed every {kflush} steps")
     kb.emit_tma_issue("bw_issue")
-
-    # ---- restep and backward step as device functions over register tiles ----
-    sz = lambda s: (t.R if s[0] else 1) * (t.C if s[1] else 1)
 
     w(f'extern "C" __global__ void __launch_bounds__({t.NT}, 1)')
     w.open(f"{kname}({', '.join(kb.param_decl)})")
@@ -928,9 +1121,11 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     kb.emit_thread_ids()
     w("u64* full = (u64*)smem;        // [0],[1]: staged inputs   [2]: checkpoint copy")
     w(f"unsigned char* stage = smem + {off_stage};")
-    w(f"float* slots = (float*)(smem + {off_slots});")
+    w(f"float* wk = (float*)(smem + {off_wk});")
+    if nphys:
+        w(f"float* slots = (float*)(smem + {off_slots});")
     if redw:
-        w(f"float* red = (float*)(smem + {off_red});")
+        w(f"float* ring = (float*)(smem + {off_ring});")
     has_tma = bool(kb.tma_items)
     w.open("if (tid == 0)")
     w("frnn_mbar_init(&full[0], 1); frnn_mbar_init(&full[1], 1); frnn_mbar_init(&full[2], 1); frnn_mbar_init_fence();")
@@ -938,8 +1133,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     w("frnn_block_sync();")
     kb.emit_plain_decl()
     tma_call = (", " + kb.tma_issue_call) if has_tma else ""
-
-    ckspec = TensorSpec((p.B, p.H, nck, p.M, p.N), _contig((p.B, p.H, nck, p.M, p.N)), DT_F32)
+    ckspec = TensorSpec((p.B, p.H, nck_store, p.M, p.N), _contig((p.B, p.H, nck_store, p.M, p.N)), DT_F32)
 
     def ck_fetch(kexpr: str, physexpr: str):
         """Start the copy of checkpoint ``kexpr`` into physical slot ``physexpr``."""
@@ -957,23 +1151,22 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 w(f"for (int e = tid; e < {slot_elems}; e += {t.NT}) "
                   f"slots[((long)({physexpr}) * {ns} + {k}) * {slot_elems} + e] = ck{k}[{base} + e];")
 
-    first_k = nck - 1
-    nv_first = p.T - first_k * D
+    first_c = nchunk - 1
+    nv_first = p.T - first_c * D
     if kb.plain_items:
-        kb.emit_plain_load(str(first_k * D), str(nv_first))
+        kb.emit_plain_load(str(first_c * D), str(nv_first))
         kb.emit_plain_store("stage")
     if has_tma:
         w.open("if (warp == 0)")
-        w(f"bw_issue(stage, &full[0], {first_k * D}, {nv_first}, lane, b, h, m0{tma_call});")
-        if nck > 1:
-            w(f"bw_issue(stage + {stage_bytes}, &full[1], {(first_k - 1) * D}, {D}, lane, b, h, m0{tma_call});")
+        w(f"bw_issue(stage, &full[0], {first_c * D}, {nv_first}, lane, b, h, m0{tma_call});")
+        if nchunk > 1:
+            w(f"bw_issue(stage + {stage_bytes}, &full[1], {(first_c - 1) * D}, {D}, lane, b, h, m0{tma_call});")
         w.close()
-    ck_fetch(str(first_k), "0")
-    w("frnn_block_sync();")
+    if not rev:
+        ck_fetch(str(first_c), "0")
 
-    body = Body(w, t, g_bw.shape)
-    body.shape.update(g_re.shape)
-    # d_state registers, seeded with the gradient of the final state (contiguous [B,H,M,N])
+    body = Body(w, t, g_bw2.shape)
+    body.shape.update(g_aux2.shape)
     dshape = (p.B, p.H, p.M, p.N)
     for k in range(ns):
         body.declare(dnext_names[k], stcls)
@@ -983,18 +1176,111 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         body.declare(p.st_names[k], stcls)
     for i in const_inputs:
         kb.emit_const_input(body, p.in_names[i], p.in_cls(i), p.inputs[i], f"in{i}", IN_DIMS)
-    # accumulators for gradients of time-invariant inputs
     for go in grads:
         if go.over_t and go.cls == M1:
             w(f"float gacc{go.index}[{t.R}];")
-            w(f"#pragma unroll")
+            w("#pragma unroll")
             w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] = 0.0f;")
+    # time-invariant per-column / per-head gradients: thread e accumulates element e over time
+    tinv = [go for go in pm_vec + pm_sc if go.over_t]
     nred_per_thread = (redw + t.NT - 1) // t.NT if redw else 0
-    if any(go.over_t and go.cls != M1 for go in grads):
+    if tinv:
         w(f"float racc[{max(1, nred_per_thread)}];")
-        w(f"#pragma unroll")
+        w("#pragma unroll")
         w(f"for (int q = 0; q < {max(1, nred_per_thread)}; q++) racc[q] = 0.0f;")
-    w("int rpar = 0; (void)rpar;")
+    w("int rcnt = 0, rhalf = 0, rt_first = 0; (void)rcnt; (void)rhalf; (void)rt_first;")
+
+    # element offsets inside one ring row
+    ring_off: Dict[int, int] = {}
+    pos = 0
+    for go in pm_vec:
+        ring_off[go.index] = pos
+        pos += p.N
+    for go in pm_sc:
+        ring_off[go.index] = pos
+        pos += 1
+
+    def emit_flush():
+        """Reduce the collected steps over the row groups and write the gradients."""
+        if not redw:
+            return
+        w.open("if (rcnt > 0)")
+        w("frnn_block_sync();   // all partials of this group are in the ring")
+        w(f"const float* rr = ring + rhalf * {kflush * step_floats};")
+        nq = p.N // vw
+        stream_vec = [go for go in pm_vec if not go.over_t]
+        if stream_vec:
+            w(f"for (int it = tid; it < rcnt * {len(stream_vec) * nq}; it += {t.NT}) {{")
+            w.ind += 1
+            w(f"const int s = it / {len(stream_vec) * nq}, rem = it % {len(stream_vec) * nq}, vi = rem / {nq}, c0 = (rem % {nq}) * {vw};")
+            w(f"const int tt = rt_first - s; (void)tt;")
+            w(f"float a[{vw}];")
+            w("#pragma unroll")
+            w(f"for (int q = 0; q < {vw}; q++) a[q] = 0.0f;")
+            w("int ro = 0;")
+            for k, go in enumerate(stream_vec):
+                w(f"if (vi == {k}) ro = {ring_off[go.index]};")
+            w(f"const float* src = rr + s * {step_floats} + ro + c0;")
+            w("#pragma unroll 4")
+            w.open(f"for (int gi = 0; gi < {t.RG}; gi++)")
+            w(f"float v[{vw}];")
+            w(f"frnn_ldv<0,{vw}>(src, gi * {redw_pad}, v);")
+            w("#pragma unroll")
+            w(f"for (int q = 0; q < {vw}; q++) a[q] += v[q];")
+            w.close()
+            for k, go in enumerate(stream_vec):
+                w.open(f"if (vi == {k})")
+                idx = _elem_off(go.spec, [(0, "b"), (1, "tt"), (2, "h")])
+                sn = go.spec.st(4)
+                if go.atomic:
+                    w("#pragma unroll")
+                    w(f"for (int q = 0; q < {vw}; q++) frnn_atomic_add((float*)dx{go.index} + ({idx} + (long)(c0 + q) * {sn}L), a[q]);")
+                elif sn == 1 and go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % (vw * ELT[go.spec.dt]) == 0 for d in (0, 1, 2)):
+                    w(f"frnn_stv<{go.spec.dt},{vw}>(dx{go.index}, {idx} + c0, a);")
+                else:
+                    w("#pragma unroll")
+                    w(f"for (int q = 0; q < {vw}; q++) frnn_io<{go.spec.dt}>::st(dx{go.index}, {idx} + (long)(c0 + q) * {sn}L, a[q]);")
+                w.close()
+            w.ind -= 1
+            w("}")
+        stream_sc = [go for go in pm_sc if not go.over_t]
+        if stream_sc:
+            w(f"for (int it = tid; it < rcnt * {len(stream_sc)}; it += {t.NT}) {{")
+            w.ind += 1
+            w(f"const int s = it / {len(stream_sc)}, si = it % {len(stream_sc)}, tt = rt_first - s; (void)tt;")
+            w("int ro = 0;")
+            for k, go in enumerate(stream_sc):
+                w(f"if (si == {k}) ro = {ring_off[go.index]};")
+            w("float a = 0.0f;")
+            w(f"for (int gi = 0; gi < {t.RG}; gi++) a += rr[s * {step_floats} + gi * {redw_pad} + ro];")
+            for k, go in enumerate(stream_sc):
+                w.open(f"if (si == {k})")
+                idx = _elem_off(go.spec, [(0, "b"), (1, "tt"), (2, "h")])
+                if go.atomic:
+                    w(f"frnn_atomic_add((float*)dx{go.index} + ({idx}), a);")
+                else:
+                    w(f"frnn_io<{go.spec.dt}>::st(dx{go.index}, {idx}, a);")
+                w.close()
+            w.ind -= 1
+            w("}")
+        if tinv:
+            w("#pragma unroll")
+            w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
+            w(f"const int e = tid + q * {t.NT};")
+            conds = " || ".join(f"(e >= {ring_off[go.index]} && e < {ring_off[go.index] + (p.N if go.cls == N1 else 1)})" for go in tinv)
+            w.open(f"if ({conds})")
+            w("float a = 0.0f;")
+            w("for (int s = 0; s < rcnt; s++)")
+            w(f"  for (int gi = 0; gi < {t.RG}; gi++) a += rr[s * {step_floats} + gi * {redw_pad} + e];")
+            w("racc[q] += a;")
+            w.close()
+            w.close()
+        if ring_bufs == 1:
+            w("frnn_block_sync();   // single ring: readers done before the next group is written")
+        else:
+            w("rhalf ^= 1;")
+        w("rcnt = 0;")
+        w.close()
 
     def slot_rw(physexpr: str, store: bool):
         for k in range(ns):
@@ -1010,25 +1296,108 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                     w(f"{fn}<0,{cnt}>(slots, {idx}, &{arr}[r * {t.C} + {j * t.V + q * cnt}]);")
             w.close()
 
+    def read_wk_inputs(sub: Body, g: StepGraph):
+        used_g = dict(zip(g.inputs, g.used_inputs()))
+        for nm in g.inputs:
+            if nm in kb.wk and used_g.get(nm, False):
+                kb.emit_wk_read(sub, nm, "wkt")
+
     def emit_restep(tlexpr: str):
         w.open("")
         w(f"const int tl = {tlexpr};")
+        w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
         sub = Body(w, t, body.shape)
-        for it in kb.items:
-            if it.key in g_re.inputs and g_re.used_inputs()[g_re.inputs.index(it.key)]:
-                kb.emit_item_read(sub, it, "sp", it.key)
-        sub.graph(g_re)
+        read_wk_inputs(sub, g_aux2)
+        sub.graph(g_aux2)
         for k in range(ns):
-            o = g_re.outputs[k]
+            o = g_aux2.outputs[k]
             sub.loops(stcls, lambda r, c, k=k, o=o: f"{body.at(p.st_names[k], r, c)} = {sub.at(o, r, c)};")
         w.close()
 
+    def emit_unstep():
+        """S_t = S_{t+1} -/+ X_t (reverse mode); expects tl, wkt in scope."""
+        w.open("")
+        sub = Body(w, t, body.shape)
+        read_wk_inputs(sub, g_aux2)
+        sub.graph(g_aux2)
+        for k in range(ns):
+            o = g_aux2.outputs[k]
+            sgn = "-" if reverse.sign[k] > 0 else "+"
+            sub.loops(stcls, lambda r, c, k=k, o=o, sgn=sgn:
+                      f"{body.at(p.st_names[k], r, c)} = {body.at(p.st_names[k], r, c)} {sgn} {sub.at(o, r, c)};")
+        w.close()
+
+    def emit_bw_step():
+        """The backward step proper; expects tl, t, wkt in scope."""
+        sub = Body(w, t, body.shape)
+        read_wk_inputs(sub, g_bw2)
+        if alias_next:
+            # phase 1 (state registers hold S_{t+1}): every node that does not need S_t
+            for k, nm in enumerate(alias_next):
+                sub.alias[nm] = p.st_names[k]
+                sub.shape[nm] = stcls
+            dep_cur = g_bw2.depends_on(p.st_names)
+            for n in g_bw2.nodes:
+                if n.name not in dep_cur:
+                    sub.node(n, True)
+            emit_unstep()
+            for n in g_bw2.nodes:
+                if n.name in dep_cur:
+                    sub.node(n, True)
+        else:
+            if rev:
+                emit_unstep()
+            sub.graph(g_bw2, allow_over_m=True)
+        outs = g_bw2.outputs
+        for go in grads:
+            if go.cls != M1:
+                continue
+            val = go.value
+            if sub.partial.get(val, False):
+                raise LoweringError("per-row gradient came out as a sum over rows")
+            w(f"float gv{go.index}[{t.R}];")
+            w("#pragma unroll")
+            w(f"for (int r = 0; r < {t.R}; r++) gv{go.index}[r] = {sub.at(val, 'r', '0')};")
+            if go.over_t:
+                w("#pragma unroll")
+                w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] += gv{go.index}[r];")
+            else:
+                idx0 = _elem_off(go.spec, [(0, "b"), (1, "t"), (2, "h")])
+                kb.emit_row_vec_store(f"gv{go.index}", go.spec.dt, f"dx{go.index}", idx0, go.spec.st(3),
+                                      go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)),
+                                      atomic=go.atomic)
+        if redw:
+            w("if (rcnt == 0) rt_first = t;")
+            w(f"float* rb = ring + (rhalf * {kflush} + rcnt) * {step_floats} + rg * {redw_pad};")
+            for go in pm_vec:
+                val = go.value
+                is_pm = sub.partial.get(val, False)
+                w(f"float pv{go.index}[{t.C}];")
+                w("#pragma unroll")
+                if is_pm:
+                    w(f"for (int c = 0; c < {t.C}; c++) pv{go.index}[c] = {sub.at(val, '0', 'c')};")
+                else:
+                    w(f"for (int c = 0; c < {t.C}; c++) pv{go.index}[c] = (rg == 0) ? {sub.at(val, '0', 'c')} : 0.0f;")
+                cnt = _pick_cnt(t.V, DT_F32, p.N)
+                for j in range(t.NCH):
+                    for q in range(t.V // cnt):
+                        w(f"frnn_stv<0,{cnt}>(rb, {ring_off[go.index]} + cb + {j * t.V * t.L + q * cnt}, &pv{go.index}[{j * t.V + q * cnt}]);")
+            for go in pm_sc:
+                val = go.value
+                is_pm = sub.partial.get(val, False)
+                gate = "" if is_pm else "(rg == 0) ? "
+                tail = "" if is_pm else " : 0.0f"
+                w(f"if (l == 0) rb[{ring_off[go.index]}] = {gate}{sub.at(val, '0', '0')}{tail};")
+            w("rcnt++;")
+        for k in range(ns):
+            o = outs[nin + k]
+            sub.loops(stcls, lambda r, c, k=k, o=o: f"{body.at(dnext_names[k], r, c)} = {sub.at(o, r, c)};")
+
+    # ------------------------------------------------------------------ chunk loop
     w("#pragma unroll 1")
-    w.open(f"for (int c = 0; c < {nck}; c++)")
-    w(f"const int kc = {nck - 1} - c, t0 = kc * {D}, nv = min({D}, {p.T} - t0), buf = c & 1, par = c & 1;")
-    w(f"const int nseg = (nv + {seg - 1}) / {seg};")
+    w.open(f"for (int c = 0; c < {nchunk}; c++)")
+    w(f"const int kc = {nchunk - 1} - c, t0 = kc * {D}, nv = min({D}, {p.T} - t0), buf = c & 1;")
     w(f"unsigned char* sp = stage + buf * {stage_bytes};")
-    w(f"#define PHYS(j) (par ? ({nphys - 1} - (j)) : (j))")
     if kb.plain_items:
         w("if (kc > 0) {")
         w.ind += 1
@@ -1037,170 +1406,116 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w("}")
     if has_tma:
         w(f"if (!frnn_mbar_wait(&full[buf], (c >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
-    if ck_tma:
-        w(f"if (!frnn_mbar_wait(&full[2], c & 1, err, {ERR_CKPT_TIMEOUT})) return;")
-    # phase A: rebuild the segment bases
-    slot_rw("PHYS(0)", store=False)
-    w("#pragma unroll 1")
-    w.open("for (int j = 1; j < nseg; j++)")
-    w("#pragma unroll 1")
-    w.open(f"for (int i = 0; i < {seg}; i++)")
-    emit_restep(f"(j - 1) * {seg} + i")
-    w.close()
-    slot_rw("PHYS(j)", store=True)
-    w.close()
-    # phase B: walk the chunk backwards
-    w("#pragma unroll 1")
-    w.open(f"for (int j = {nphys - 1}; j >= 0; j--)")
-    w.open("if (j < nseg)")
-    w(f"const int seglen = min({seg}, nv - j * {seg});")
-    w("#pragma unroll 1")
-    w.open("for (int i = seglen - 1; i >= 0; i--)")
-    slot_rw("PHYS(j)", store=False)
-    w("#pragma unroll 1")
-    w.open("for (int i2 = 0; i2 < i; i2++)")
-    emit_restep(f"j * {seg} + i2")
-    w.close()
-    # ---- the backward step proper
-    w.open("")
-    w(f"const int tl = j * {seg} + i, t = t0 + tl;")
-    sub = Body(w, t, body.shape)
-    bw_used = dict(zip(g_bw.inputs, g_bw.used_inputs()))
-    for it in kb.items:
-        if bw_used.get(it.key, False):
-            kb.emit_item_read(sub, it, "sp", it.key)
-    sub.graph(g_bw, allow_over_m=True)
-    outs = g_bw.outputs
-    # per-row gradients (inputs that vary over rows)
-    for go in grads:
-        if go.cls != M1:
-            continue
-        val = go.value
-        if sub.partial.get(val, False):
-            raise LoweringError("per-row gradient came out as a sum over rows")
-        w(f"float gv{go.index}[{t.R}];")
-        w("#pragma unroll")
-        w(f"for (int r = 0; r < {t.R}; r++) gv{go.index}[r] = {sub.at(val, 'r', '0')};")
-        if go.over_t:
-            w("#pragma unroll")
-            w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] += gv{go.index}[r];")
-        else:
-            idx0 = _elem_off(go.spec, [(0, "b"), (1, "t"), (2, "h")])
-            kb.emit_row_vec_store(f"gv{go.index}", go.spec.dt, f"dx{go.index}", idx0, go.spec.st(3),
-                                  go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)),
-                                  atomic=go.atomic)
-    # per-column / per-head gradient partials -> exchange buffer
-    if redw:
-        if red_bufs == 1:
-            w("frnn_block_sync();   // single exchange buffer: the previous step's readers must be done")
-        w(f"float* rb = red + rpar * {t.RG * redw_pad} + rg * {redw_pad};")
-        for vi, go in enumerate(pm_vec):
-            val = go.value
-            is_pm = sub.partial.get(val, False)
-            w(f"float pv{vi}[{t.C}];")
-            w("#pragma unroll")
-            if is_pm:
-                w(f"for (int c = 0; c < {t.C}; c++) pv{vi}[c] = {sub.at(val, '0', 'c')};")
-            else:
-                # not a sum over rows (e.g. identically zero): only row group 0 contributes
-                w(f"for (int c = 0; c < {t.C}; c++) pv{vi}[c] = (rg == 0) ? {sub.at(val, '0', 'c')} : 0.0f;")
-            cnt = _pick_cnt(t.V, DT_F32, p.N)
-            for j in range(t.NCH):
-                for q in range(t.V // cnt):
-                    w(f"frnn_stv<0,{cnt}>(rb, {vi * p.N} + cb + {j * t.V * t.L + q * cnt}, &pv{vi}[{j * t.V + q * cnt}]);")
-        for si, go in enumerate(pm_sc):
-            val = go.value
-            is_pm = sub.partial.get(val, False)
-            gate = "" if is_pm else "(rg == 0) ? "
-            tail = "" if is_pm else " : 0.0f"
-            w(f"if (l == 0) rb[{len(pm_vec) * p.N + si}] = {gate}{sub.at(val, '0', '0')}{tail};")
-    # d_state for the previous step
-    nin_bw = len(p.inputs)
-    for k in range(ns):
-        o = outs[nin_bw + k]
-        sub.loops(stcls, lambda r, c, k=k, o=o: f"{body.at(dnext_names[k], r, c)} = {sub.at(o, r, c)};")
-    if redw:
-        w("frnn_block_sync();")
-        w(f"const float* rr = red + rpar * {t.RG * redw_pad};")
-        w("#pragma unroll")
-        w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
-        w(f"const int e = tid + q * {t.NT};")
-        w.open(f"if (e < {redw})")
-        w("float a = 0.0f;")
-        w("#pragma unroll 4")
-        w(f"for (int gi = 0; gi < {t.RG}; gi++) a += rr[gi * {redw_pad} + e];")
-        # dispatch on which gradient element e belongs to
-        lo = 0
-        for go in pm_vec + pm_sc:
-            n_el = p.N if go.cls == N1 else 1
-            cond = f"e >= {lo} && e < {lo + n_el}" if len(pm_vec) + len(pm_sc) > 1 else "true"
-            w.open(f"if ({cond})")
-            j = f"(e - {lo})"
-            if go.over_t:
-                w("racc[q] += a;")
-            else:
-                dims = [(0, "b"), (1, "t"), (2, "h")] + ([(4, j)] if go.cls == N1 else [])
-                idx = _elem_off(go.spec, dims)
-                if go.atomic:
-                    w(f"frnn_atomic_add((float*)dx{go.index} + ({idx}), a);")
-                else:
-                    w(f"frnn_io<{go.spec.dt}>::st(dx{go.index}, {idx}, a);")
-            w.close()
-            lo += n_el
-        w.close()
-        w.close()
-        if red_bufs == 2:
-            w("rpar ^= 1;")
-    w.close()   # backward step scope
-    w.close()   # i loop
-    w.close()   # if j < nseg
-    # the highest physical slot of this parity is free now: fetch the next checkpoint into it
-    w.open(f"if (j == {nphys - 1} && kc > 0)")
-    w("frnn_block_sync();")
-    ck_fetch("kc - 1", f"PHYS({nphys - 1})")
-    w.close()
-    w.close()   # j loop
+    w("frnn_block_sync();   // previous chunk's work buffer is no longer read")
+    kb.emit_convert("sp", "wk", "nv")
     if kb.plain_items:
         w("if (kc > 0) {")
         w.ind += 1
         kb.emit_plain_store(f"(stage + (buf ^ 1) * {stage_bytes})")
         w.ind -= 1
         w("}")
-    w("frnn_block_sync();")
+    w("frnn_block_sync();   // work buffer complete; the raw buffer may be refilled")
     if has_tma:
         w.open("if (warp == 0 && kc >= 2)")
         w(f"bw_issue(sp, &full[buf], (kc - 2) * {D}, {D}, lane, b, h, m0{tma_call});")
         w.close()
-    w("#undef PHYS")
+
+    if rev:
+        # reload an exact forward state at the end of this chunk when it is a checkpoint boundary
+        w.open(f"if (c == 0 || (t0 + nv) % {dck} == 0)")
+        w(f"const int kck = (c == 0) ? {nck} : (t0 + nv) / {dck};")
+        for k in range(ns):
+            base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, "kck")])
+            kb.emit_tile_global(vname(p.st_names[k]), ckspec, f"ck{k}", base, 3, 4, load=True)
+        w.close()
+        kf = max(1, kflush)
+        w("#pragma unroll 1")
+        w.open(f"for (int g1 = nv; g1 > 0; g1 -= {kf})")
+        w(f"const int g0 = max(g1 - {kf}, 0);")
+        w(f"#pragma unroll {step_unroll}")
+        w.open("for (int tl = g1 - 1; tl >= g0; tl--)")
+        w("const int t = t0 + tl; (void)t;")
+        w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
+        w.open("")
+        emit_bw_step()
+        w.close()
+        w.close()
+        emit_flush()
+        w.close()
+    else:
+        w(f"const int par = c & 1, nseg = (nv + {seg - 1}) / {seg};")
+        w(f"#define PHYS(j) (par ? ({nphys - 1} - (j)) : (j))")
+        if ck_tma:
+            w(f"if (!frnn_mbar_wait(&full[2], c & 1, err, {ERR_CKPT_TIMEOUT})) return;")
+        # phase A: rebuild the segment bases
+        slot_rw("PHYS(0)", store=False)
+        w("#pragma unroll 1")
+        w.open("for (int j = 1; j < nseg; j++)")
+        w("#pragma unroll 1")
+        w.open(f"for (int i = 0; i < {seg}; i++)")
+        emit_restep(f"(j - 1) * {seg} + i")
+        w.close()
+        slot_rw("PHYS(j)", store=True)
+        w.close()
+        # phase B: walk the chunk backwards
+        w("#pragma unroll 1")
+        w.open(f"for (int j = {nphys - 1}; j >= 0; j--)")
+        w.open("if (j < nseg)")
+        w(f"const int seglen = min({seg}, nv - j * {seg});")
+        w("#pragma unroll 1")
+        w.open("for (int i = seglen - 1; i >= 0; i--)")
+        slot_rw("PHYS(j)", store=False)
+        w("#pragma unroll 1")
+        w.open("for (int i2 = 0; i2 < i; i2++)")
+        emit_restep(f"j * {seg} + i2")
+        w.close()
+        w.open("")
+        w(f"const int tl = j * {seg} + i, t = t0 + tl; (void)t;")
+        w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
+        emit_bw_step()
+        w.close()
+        if redw and kflush > 1:
+            w(f"if (rcnt == {kflush}) {{")
+            w.ind += 1
+            emit_flush()
+            w.ind -= 1
+            w("}")
+        elif redw:
+            emit_flush()
+        w.close()   # i loop
+        w.close()   # if j < nseg
+        w.open(f"if (j == {nphys - 1} && kc > 0)")
+        w("frnn_block_sync();   // every thread is done with the slot that is overwritten next")
+        ck_fetch("kc - 1", f"PHYS({nphys - 1})")
+        w.close()
+        w.close()   # j loop
+        if redw and kflush > 1:
+            emit_flush()
+        w("#undef PHYS")
     w.close()   # chunk loop
 
-    # d_initial_state, laid out like the initial state
     for k in range(ns):
         kb.emit_tile_global(vname(dnext_names[k]), p.states[k], f"ds0_{k}",
                             _elem_off(p.states[k], [(0, "b"), (1, "h")]), 2, 3, load=False)
-    # gradients of time-invariant inputs
     for go in grads:
-        if not go.over_t:
-            continue
-        if go.cls == M1:
+        if go.over_t and go.cls == M1:
             idx0 = _elem_off(go.spec, [(0, "b"), (2, "h")])
             kb.emit_row_vec_store(f"gacc{go.index}", DT_F32, f"dx{go.index}", idx0, go.spec.st(3), False, atomic=True)
-    if any(go.over_t and go.cls != M1 for go in grads):
+    if tinv:
         w("#pragma unroll")
         w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
         w(f"const int e = tid + q * {t.NT};")
-        lo = 0
-        for go in pm_vec + pm_sc:
+        for go in tinv:
+            lo = ring_off[go.index]
             n_el = p.N if go.cls == N1 else 1
-            if go.over_t:
-                w.open(f"if (e >= {lo} && e < {lo + n_el})")
-                dims = [(0, "b"), (2, "h")] + ([(4, f"(e - {lo})")] if go.cls == N1 else [])
-                w(f"frnn_atomic_add((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
-                w.close()
-            lo += n_el
+            w.open(f"if (e >= {lo} && e < {lo + n_el})")
+            dims = [(0, "b"), (2, "h")] + ([(4, f"(e - {lo})")] if go.cls == N1 else [])
+            w(f"frnn_atomic_add((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
+            w.close()
         w.close()
     w.close()
     return KernelSource(kname, w.text(), (1, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
-                        {"stage_bytes": stage_bytes, "slot_bytes": slot_bytes, "red_bytes": red_bytes,
-                         "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
-                         "nck": nck, "D": D, "ck_tma": ck_tma})
+                        {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
+                         "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
+                         "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
+                         "reverse": rev, "hoisted": [n.name for n in kb.hoisted]})

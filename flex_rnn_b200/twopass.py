@@ -76,15 +76,21 @@ def verify_meta(a, b, msg=""):
 @dataclass
 class Tuning:
     """Code-generation parameters (defaults picked by ``default_tuning``)."""
-    fw_r: int = 4
-    fw_c: int = 16
+    fw_r: int = 4            # forward tile: rows x columns per thread, rows per CTA
+    fw_c: int = 32
     fw_mb: int = 32
-    fw_stage: int = 16
+    fw_stage: int = 16       # timesteps per staged chunk (forward)
     fw_min_blocks: int = 1
-    bw_r: int = 8
+    bw_r: int = 8            # backward tile
     bw_c: int = 8
-    seg: int = 4
+    seg: int = 4             # generic backward: steps per segment, segments (slots) per checkpoint chunk
     nslots: int = 2
+    kflush: int = 4          # steps of gradient partials reduced together (lowered until shared memory fits)
+    reverse: int = 1         # use the reverse re-step when the state update is additive
+    rev_stage: int = 8       # reverse mode: timesteps per staged chunk
+    rev_resync: int = 4      # reverse mode: chunks between exact checkpoints
+    fw_unroll: int = 2       # unroll factor of the timestep loops
+    bw_unroll: int = 2
     use_tma: bool = True
 
 
@@ -107,6 +113,7 @@ def default_tuning(B, T, H, M, N, nstates) -> Tuning:
     while tu.seg * tu.nslots > T and tu.seg > 1:
         tu.seg -= 1
     tu.fw_stage = max(1, min(tu.fw_stage, T))
+    tu.rev_stage = max(1, min(tu.rev_stage, T))
     return tu
 
 
@@ -126,10 +133,12 @@ class Plan:
     tuning: Tuning
     fw_tile: lower.Tile
     bw_tile: lower.Tile
-    D: int
-    nck: int
+    D: int                  # checkpoint interval (timesteps)
+    nck: int                # checkpoints stored per (b,h)
     k_fwd: int
     k_joint: int
+    reverse: Optional[lower.Reverse] = None
+    bw_choice: Tuple[int, int, int] = (4, 1, 2)   # (seg or reverse stage, kflush, ring buffers) that fit shared memory
 
 
 def _spec(t: th.Tensor) -> TensorSpec:
@@ -208,19 +217,33 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     tu = tuning or default_tuning(B, T, H, M, N, nst)
     fw_tile = choose_tile(M, N, tu.fw_r, tu.fw_c, tu.fw_mb)
     bw_tile = choose_tile(M, N, tu.bw_r, tu.bw_c, None)
-    D = tu.seg * tu.nslots
-    nck = (T + D - 1) // D
-
-    dev = inputs[0].device if inputs else state[0].device
-    # declared outputs (what the fake implementations materialise)
-    out_meta = tuple(th.empty(B, T, H, M, dtype=d, device="meta") for d in out_dtypes)
-    stT_meta = tuple(th.empty_like(s, device="meta") for s in state)
-    store_meta = tuple(th.empty(B, H, nck, M, N, dtype=th.float32, device="meta") for _ in state)
-    aux_meta = (th.empty(len(aux), B, H, T, M, dtype=th.float32, device="meta"),)
+    # additive state update S' = S +/- X with X free of the state (given the saved row sums):
+    # the backward can step the state backwards instead of recomputing it from checkpoints
+    reverse = None
+    if tu.reverse:
+        dep = g_re.depends_on(st_names)
+        prod = g_re.node_map()
+        incs, signs = [], []
+        for k, nm in enumerate(ns_names):
+            n = prod.get(nm)
+            if n is None or n.op not in ("add", "sub") or len(n.args) != 2:
+                break
+            a, b = n.args
+            if a == st_names[k] and isinstance(b, str) and b not in dep and b not in st_names:
+                incs.append(b)
+                signs.append(1 if n.op == "add" else -1)
+            elif n.op == "add" and b == st_names[k] and isinstance(a, str) and a not in dep and a not in st_names:
+                incs.append(a)
+                signs.append(1)
+            else:
+                break
+        if len(incs) == nst:
+            g_x = joint.pruned(incs, "unstep", leaves=aux)
+            reverse = lower.Reverse(g_x, signs, max(1, tu.rev_resync))
+    dy_names, dnext_names = list(dy_names), list(dnext_names)
+    prob = Problem(B, T, H, M, N, [_spec(x) for x in inputs], list(in_names), [_spec(s) for s in state],
+                   list(st_names), [_DT[d] for d in out_dtypes], len(aux))
     dx_meta = tuple(th.empty_like(x, device="meta") for x in inputs)
-    fw_meta = get_meta([*out_meta, *stT_meta, *store_meta, *aux_meta])
-    bw_meta = get_meta([*dx_meta, *stT_meta])
-
     grads: List[GradOut] = []
     for i, x in enumerate(inputs):
         cls = in_cls[i]
@@ -233,31 +256,79 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             spec = TensorSpec(tuple(gm.shape), tuple(gm.stride()), _DT[gm.dtype], True)
         grads.append(GradOut(i, cls, spec, dx_names[i], over_t, atomic))
 
-    prob = Problem(B, T, H, M, N, [_spec(x) for x in inputs], list(in_names), [_spec(s) for s in state],
-                   list(st_names), [_DT[d] for d in out_dtypes], len(aux))
+    # pick the backward's staging / flush parameters that fit shared memory
+    choice = None
+    seg0 = tu.rev_stage if reverse is not None else tu.seg
+    for sg in range(seg0, 0, -1):
+        k = max(1, tu.kflush)
+        cands = []
+        while k >= 1:
+            cands += [(k, 2), (k, 1)]
+            k //= 2
+        for kflush, bufs in cands:
+            try:
+                ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, tu.nslots,
+                                   tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
+            except lower.LoweringError:
+                if any(g.cls == MN for g in grads):
+                    ks = None
+                    break
+                raise
+            if ks.smem_bytes <= SMEM_LIMIT:
+                choice = (sg, kflush, bufs)
+                break
+        if choice or ks is None:
+            break
+    if choice is None:
+        if any(g.cls == MN for g in grads):
+            choice = (seg0, 1, 1)
+        else:
+            raise lower.LoweringError(f"the backward kernel of a {M}x{N} state does not fit shared memory")
+    if reverse is not None:
+        D = choice[0] * reverse.resync
+        nck = (T + D - 1) // D + 1          # plus the final state
+    else:
+        D = choice[0] * tu.nslots
+        nck = (T + D - 1) // D
+
+    dev = inputs[0].device if inputs else state[0].device
+    # declared outputs (what the fake implementations materialise)
+    out_meta = tuple(th.empty(B, T, H, M, dtype=d, device="meta") for d in out_dtypes)
+    stT_meta = tuple(th.empty_like(s, device="meta") for s in state)
+    store_meta = tuple(th.empty(B, H, nck, M, N, dtype=th.float32, device="meta") for _ in state)
+    aux_meta = (th.empty(len(aux), B, H, T, M, dtype=th.float32, device="meta"),)
+    fw_meta = get_meta([*out_meta, *stT_meta, *store_meta, *aux_meta])
+    bw_meta = get_meta([*dx_meta, *stT_meta])
+
     plan = Plan(prob, joint, g_fw, g_re, g_bw, aux, nout, nst, grads, tu, fw_tile, bw_tile, D, nck,
-                g_fw0.count_mn_ops(), joint.pruned(jout, "all").count_mn_ops())
-    plan.dy_names, plan.dnext_names = list(dy_names), list(dnext_names)   # type: ignore[attr-defined]
+                g_fw0.count_mn_ops(), joint.pruned(jout, "all").count_mn_ops(), reverse, choice)
+    plan.dy_names, plan.dnext_names = dy_names, dnext_names   # type: ignore[attr-defined]
     return plan, fw_meta, bw_meta
 
 
 def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
     """Emit the CUDA source of the forward and the backward kernel."""
     p, tu = plan.problem, plan.tuning
-    fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, plan.fw_tile, tu.fw_stage, plan.D, tu.use_tma,
-                      tu.fw_min_blocks, prelude())
+    rev = plan.reverse
+    # forward: keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
+    stage = tu.fw_stage
+    while True:
+        fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, plan.fw_tile, stage, plan.D, tu.use_tma,
+                          tu.fw_min_blocks, prelude(), final_ckpt=rev is not None, step_unroll=tu.fw_unroll)
+        ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
+        per_sm = min(max(1, -(-ncta // 148)), 2048 // fw.block, 32)
+        if stage <= 4 or fw.smem_bytes * per_sm <= 200 * 1024:
+            break
+        stage //= 2
     if any(g.cls == MN for g in plan.grads):
         raise lower.LoweringError("matrix-per-head inputs are not supported yet")
-    bw = None
-    for red_bufs in (2, 1):
-        bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, [], plan.dy_names,   # type: ignore[attr-defined]
-                           plan.dnext_names, plan.bw_tile, tu.seg, tu.nslots, tu.use_tma, prelude(),        # type: ignore[attr-defined]
-                           red_bufs=red_bufs)
-        if bw.smem_bytes <= SMEM_LIMIT:
-            break
-    for k in (fw, bw):
-        if k.smem_bytes > SMEM_LIMIT:
-            raise lower.LoweringError(f"kernel {k.name} needs {k.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
+    sg, kflush, bufs = plan.bw_choice
+    bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
+                       plan.dnext_names, plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),          # type: ignore[attr-defined]
+                       kflush=kflush, ring_bufs=bufs, reverse=rev, step_unroll=tu.bw_unroll)
+    for kk in (fw, bw):
+        if kk.smem_bytes > SMEM_LIMIT:
+            raise lower.LoweringError(f"kernel {kk.name} needs {kk.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
     return fw, bw
 
 
