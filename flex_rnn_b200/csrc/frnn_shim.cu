@@ -261,6 +261,74 @@ int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, 
 
 }  // extern "C"
 
+// ---- launch with the kernel's scratch buffers in library-owned static memory ----
+
+#define FRNN_STATIC_SCRATCH_BYTES (32u << 20)
+// Scratch for frnn_launch_static_scratch.  Lives in every CUDA context that loads
+// this library until the process exits; shared by all calls on that device.
+static __device__ __align__(256) unsigned char frnn_static_scratch[FRNN_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_scratch_mu;
+void* g_scratch_base[64] = {nullptr};   // device address of frnn_static_scratch, per device ordinal
+}
+
+extern "C" {
+
+size_t frnn_static_scratch_capacity(void) { return (size_t)FRNN_STATIC_SCRATCH_BYTES; }
+
+int frnn_launch_static_scratch(frnn_module_t m, int kernel, const unsigned grid[3], const unsigned block[3],
+                               unsigned smem_bytes, void* stream, void* const* args, int nargs,
+                               const int* scratch_arg, const size_t* scratch_bytes, int nscratch) {
+    enum { MAX_ARGS = 64 };
+    if (!m || !args || nargs <= 0 || nargs > MAX_ARGS || nscratch <= 0 || !scratch_arg || !scratch_bytes)
+        return fail(FRNN_E_ARG, "frnn_launch_static_scratch: bad argument (at most %d kernel parameters)", (int)MAX_ARGS);
+    // carve 256-byte aligned slices out of the static array; refuse what does not fit
+    size_t off[MAX_ARGS];
+    size_t total = 0;
+    for (int i = 0; i < nscratch; i++) {
+        if (scratch_arg[i] < 0 || scratch_arg[i] >= nargs)
+            return fail(FRNN_E_ARG, "frnn_launch_static_scratch: scratch parameter index %d out of range", scratch_arg[i]);
+        off[i] = total;
+        total += (scratch_bytes[i] + 255) / 256 * 256;
+        if (total > (size_t)FRNN_STATIC_SCRATCH_BYTES || scratch_bytes[i] > (size_t)FRNN_STATIC_SCRATCH_BYTES)
+            return fail(FRNN_E_ARG,
+                        "frnn_launch_static_scratch: the kernel needs more scratch than the library's static "
+                        "buffer holds (capacity %zu bytes); use frnn_launch with caller-allocated scratch",
+                        (size_t)FRNN_STATIC_SCRATCH_BYTES);
+    }
+    // one-time set-up per device: the host-side name of a __device__ array is not a device
+    // address; ask the runtime for the address in the current device's context
+    int dev = -1;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess || dev < 0 || dev >= 64)
+        return fail(FRNN_E_DRIVER, "frnn_launch_static_scratch: no current CUDA device: %s", cudaGetErrorString(ce));
+    void* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_scratch_mu);
+        if (!g_scratch_base[dev]) {
+            void* p = nullptr;
+            ce = cudaGetSymbolAddress(&p, frnn_static_scratch);
+            if (ce != cudaSuccess || !p)
+                return fail(FRNN_E_DRIVER, "frnn_launch_static_scratch: cudaGetSymbolAddress failed: %s",
+                            cudaGetErrorString(ce));
+            g_scratch_base[dev] = p;
+        }
+        base = g_scratch_base[dev];
+    }
+    // parameter list with the scratch pointers substituted (stack storage only)
+    void* slot[MAX_ARGS];
+    void* argv[MAX_ARGS];
+    for (int i = 0; i < nargs; i++) argv[i] = args[i];
+    for (int i = 0; i < nscratch; i++) {
+        slot[i] = (unsigned char*)base + off[i];
+        argv[scratch_arg[i]] = &slot[i];
+    }
+    return frnn_launch(m, kernel, grid, block, smem_bytes, stream, argv, nargs);
+}
+
+}  // extern "C"
+
 // ---- benchmark helpers --------------------------------------------------------
 
 __global__ void frnn_flush_kernel(uint4* p, size_t n16, unsigned v) {

@@ -18,7 +18,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfrnn_b200.so")
 
 SYMBOLS = ["frnn_abi_version", "frnn_last_error", "frnn_compile", "frnn_free", "frnn_module_load",
-           "frnn_module_unload", "frnn_launch", "frnn_kernel_attrs", "frnn_l2_flush", "frnn_fp32_peak_probe"]
+           "frnn_module_unload", "frnn_launch", "frnn_kernel_attrs", "frnn_l2_flush", "frnn_fp32_peak_probe",
+           "frnn_launch_static_scratch", "frnn_static_scratch_capacity"]
 
 
 class FrnnError(RuntimeError):
@@ -51,6 +52,9 @@ def lib() -> ctypes.CDLL:
         L.frnn_module_unload.argtypes = [vp]
         L.frnn_launch.argtypes = [vp, ci, ctypes.POINTER(cu), ctypes.POINTER(cu), cu, vp, ctypes.POINTER(vp), ci]
         L.frnn_kernel_attrs.argtypes = [vp, ci, ctypes.POINTER(ci), ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        L.frnn_launch_static_scratch.argtypes = [vp, ci, ctypes.POINTER(cu), ctypes.POINTER(cu), cu, vp,
+                                                 ctypes.POINTER(vp), ci, ctypes.POINTER(ci), ctypes.POINTER(sz), ci]
+        L.frnn_static_scratch_capacity.restype = sz
         L.frnn_l2_flush.argtypes = [vp, sz, vp]
         L.frnn_fp32_peak_probe.argtypes = [vp, ci, vp, ctypes.POINTER(ctypes.c_double)]
         _lib = L
@@ -122,6 +126,24 @@ class Module:
         b = (ctypes.c_uint * 3)(int(block), 1, 1)
         _check(lib().frnn_launch(self._h, kernel, g, b, int(smem), ctypes.c_void_p(int(stream)), args, n),
                f"frnn_launch({self._names[kernel]})")
+
+    def launch_static_scratch(self, kernel: int, grid: Sequence[int], block: int, smem: int, stream: int,
+                              ptrs: Sequence[int], scratch: Dict[int, int]):
+        """Like :meth:`launch`, for callers that cannot allocate device memory:
+        the parameters listed in ``scratch`` (parameter index -> bytes) are
+        pointed at the library's static scratch array; the entries of ``ptrs``
+        at those indices are ignored.  Fails if the sizes exceed the array."""
+        n = len(ptrs)
+        vals = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(p)) for p in ptrs])
+        args = (ctypes.c_void_p * n)(*[ctypes.addressof(vals) + i * ctypes.sizeof(ctypes.c_void_p) for i in range(n)])
+        g = (ctypes.c_uint * 3)(*[int(x) for x in grid])
+        b = (ctypes.c_uint * 3)(int(block), 1, 1)
+        idx = sorted(scratch)
+        sa = (ctypes.c_int * len(idx))(*idx)
+        sb = (ctypes.c_size_t * len(idx))(*[int(scratch[i]) for i in idx])
+        _check(lib().frnn_launch_static_scratch(self._h, kernel, g, b, int(smem), ctypes.c_void_p(int(stream)), args, n,
+                                                sa, sb, len(idx)),
+               f"frnn_launch_static_scratch({self._names[kernel]})")
 
     def attrs(self, kernel: int) -> Dict[str, int]:
         r, s, l = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()

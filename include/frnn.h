@@ -85,6 +85,43 @@ int frnn_launch(frnn_module_t m, int kernel, const unsigned grid[3], const unsig
  * of a loaded kernel, as the driver reports them. */
 int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, int* local_bytes);
 
+/*
+ * frnn_launch for callers that must not allocate device memory.  (No
+ * counterpart in the reference, whose host closures allocate every buffer
+ * with torch on each call.)
+ *
+ * Some callers of a compiled forward kernel only want its results - an
+ * inference server stepping a recurrent layer, a real-time loop, code running
+ * under an allocator that forbids cudaMalloc after start-up - yet the kernel
+ * also writes training-time scratch (state checkpoints, saved row sums) that
+ * such a caller would have to allocate and never read.  This entry point puts
+ * those buffers into a static device array owned by the library instead: the
+ * caller passes inputs, outputs and the error word as for frnn_launch, and
+ * names which kernel parameters are scratch (`scratch_arg[i]`, an index into
+ * `args`; what `args` holds at those indices is ignored) and how many bytes
+ * each needs (`scratch_bytes[i]`).  Each gets a 256-byte aligned slice.
+ *
+ * Limits and rules:
+ *  - the slices together must fit frnn_static_scratch_capacity() bytes
+ *    (32 MiB); a larger request fails with FRNN_E_ARG and launches nothing;
+ *  - at most 64 kernel parameters;
+ *  - every GPU on which the library is used keeps the array until the process
+ *    exits; all calls on a device share it and it keeps the previous call's
+ *    contents, so a kernel must not expect zeros there (the forward kernels
+ *    only write their scratch) and two calls whose kernels overlap in time on
+ *    one GPU race on it - keep them on one stream or serialise them;
+ *  - the first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress); make that first call before any stream capture;
+ *  - the call itself performs no cudaMalloc / cudaFree and no host heap
+ *    allocation.
+ */
+int frnn_launch_static_scratch(frnn_module_t m, int kernel, const unsigned grid[3], const unsigned block[3],
+                               unsigned smem_bytes, void* stream, void* const* args, int nargs,
+                               const int* scratch_arg, const size_t* scratch_bytes, int nscratch);
+
+/* Size in bytes of the static scratch array behind frnn_launch_static_scratch. */
+size_t frnn_static_scratch_capacity(void);
+
 /* ---- helpers compiled into the library (used by the benchmark harness) ---- */
 
 /* Overwrite `bytes` bytes at `buf` (device) with a byte pattern; writing a
