@@ -85,7 +85,7 @@ class Tuning:
     bw_c: int = 8
     seg: int = 4             # generic backward: steps per segment, segments (slots) per checkpoint chunk
     nslots: int = 2
-    kflush: int = 4          # steps of gradient partials reduced together (lowered until shared memory fits)
+    kflush: int = 8          # steps of gradient partials reduced together (lowered until shared memory fits)
     reverse: int = 1         # use the reverse re-step when the state update is additive
     rev_stage: int = 8       # reverse mode: timesteps per staged chunk
     rev_resync: int = 4      # reverse mode: chunks between exact checkpoints
