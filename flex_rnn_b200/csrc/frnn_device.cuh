@@ -64,6 +64,19 @@ FRNN_DEV void frnn_bulk_g2s(void* dst_smem, const void* src_gmem, u32 bytes, u64
         "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(frnn_smem_addr(bar))
         : "memory");
 }
+// Tiled TMA load of a 4-D box through a tensor map (cp.async.bulk.tensor, no
+// multicast).  The map is encoded on the host (frnn_tensor_map_encode) and
+// passed as a __grid_constant__ kernel parameter.  c0 (innermost coordinate)
+// times the element size must be a multiple of 16 bytes.
+struct __align__(64) frnn_tmap { unsigned long long opaque[16]; };
+#define FRNN_TMAP_PARAM const __grid_constant__ frnn_tmap
+FRNN_DEV void frnn_tma_load_4d(void* dst_smem, const frnn_tmap* map, int c0, int c1, int c2, int c3, u64* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+            frnn_smem_addr(dst_smem)),
+        "l"((u64)map), "r"(frnn_smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 FRNN_DEV bool frnn_mbar_try(u64* bar, u32 parity) {
     u32 ok;
     asm volatile(

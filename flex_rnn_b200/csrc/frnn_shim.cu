@@ -93,6 +93,9 @@ struct Driver {
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                              CUstream, void**, void**);
     CUresult (*GetErrorString)(CUresult, const char**);
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     std::string why;
 };
 
@@ -117,6 +120,7 @@ Driver* driver() {
         *(void**)&d.FuncGetAttribute = sym("cuFuncGetAttribute");
         *(void**)&d.LaunchKernel = sym("cuLaunchKernel");
         *(void**)&d.GetErrorString = sym("cuGetErrorString");
+        *(void**)&d.TensorMapEncodeTiled = sym("cuTensorMapEncodeTiled");
         if (!ok) { dlclose(d.lib); d.lib = nullptr; return; }
         d.Init(0);
     });
@@ -246,6 +250,33 @@ int frnn_launch(frnn_module_t m, int kernel, const unsigned grid[3], const unsig
     CUresult r = d->LaunchKernel(m->fn[kernel], grid[0], grid[1], grid[2], block[0], block[1], block[2], smem_bytes,
                                  (CUstream)stream, (void**)args, nullptr);
     if (r != CUDA_SUCCESS) return fail(FRNN_E_LAUNCH, "cuLaunchKernel: %s", cu_str(d, r));
+    return FRNN_OK;
+}
+
+int frnn_tensor_map_encode(void* out_map, const void* base, unsigned elt_bytes, unsigned rank,
+                           const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+    if (!out_map || !base || rank < 1 || rank > 5 || !dims || !box || (rank > 1 && !strides_bytes))
+        return fail(FRNN_E_ARG, "frnn_tensor_map_encode: bad argument");
+    if (((uintptr_t)out_map & 63) || ((uintptr_t)base & 15))
+        return fail(FRNN_E_ARG, "frnn_tensor_map_encode: the map must be 64-byte and the tensor 16-byte aligned");
+    Driver* d = driver();
+    if (!d) return fail(FRNN_E_DRIVER, "CUDA driver is not available");
+    CUtensorMapDataType dt;
+    switch (elt_bytes) {
+        case 1: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+        case 2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;
+        case 4: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;
+        case 8: dt = CU_TENSOR_MAP_DATA_TYPE_UINT64; break;
+        default: return fail(FRNN_E_ARG, "frnn_tensor_map_encode: element size %u", elt_bytes);
+    }
+    cuuint64_t gd[5], gs[5];
+    cuuint32_t bx[5], es[5];
+    for (unsigned i = 0; i < rank; i++) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+    for (unsigned i = 0; i + 1 < rank; i++) gs[i] = strides_bytes[i];
+    CUresult r = d->TensorMapEncodeTiled((CUtensorMap*)out_map, dt, rank, (void*)base, gd, gs, bx, es,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FRNN_E_DRIVER, "cuTensorMapEncodeTiled: %s", cu_str(d, r));
     return FRNN_OK;
 }
 

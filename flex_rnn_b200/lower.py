@@ -131,6 +131,7 @@ class StagedItem:
     tma: bool
     off: int = 0             # byte offset inside a stage buffer
     rowb: int = 0            # bytes per timestep inside the stage buffer
+    tmap: Optional[dict] = None   # tensor-map description when the item is fetched by one tiled TMA load per chunk
 
 
 @dataclass
@@ -143,6 +144,7 @@ class KernelSource:
     params: List[str]        # parameter names in order
     param_decl: List[str] = field(default_factory=list)   # C declarations of the parameters
     info: Dict[str, object] = field(default_factory=dict)
+    tmaps: List[dict] = field(default_factory=list)       # tensor maps to encode per launch (see KernelBuilder.plan)
 
 
 # ---------------------------------------------------------------------------
@@ -480,6 +482,7 @@ class KernelBuilder:
         self.params: List[str] = []
         self.param_decl: List[str] = []
         self.const_scalars: Dict[str, str] = {}    # time-invariant [1,1] inputs kept in registers
+        self.tensor_tma = True                     # use tiled tensor-map loads where possible
 
     # -- parameters ----------------------------------------------------------
     def add_param(self, name: str, ctype: str, const: bool):
@@ -489,8 +492,9 @@ class KernelBuilder:
         self.param_decl.append(f"{q}{ctype}*{r} {name}")
 
     # -- raw staging plan ------------------------------------------------------
-    def add_item(self, key: str, cls: Shape, spec: TensorSpec, ptr: str, dims: Dict[str, int]):
-        """``dims`` maps 'b','t','h','v' (the vector dim) to tensor dim indices."""
+    def add_item(self, key: str, cls: Shape, spec: TensorSpec, ptr: str, dims: Dict[str, int], const_off: int = 0):
+        """``dims`` maps 'b','t','h','v' (the vector dim) to tensor dim indices;
+        ``const_off`` is a constant element offset added to the tensor's base."""
         t = self.t
         length = {N1: self.p.N, M1: t.MB, S11: 1}[cls]
         inner = spec.st(dims["v"]) if cls != S11 else 1
@@ -505,7 +509,23 @@ class KernelBuilder:
                and (spec.st(dims["b"]) * e) % 16 == 0 and (spec.st(dims["h"]) * e) % 16 == 0
                and (cls != M1 or (t.MB * spec.st(dims["v"]) * e) % 16 == 0))
         rowb = (length * e + 15) // 16 * 16
-        self.items.append(StagedItem(key, cls, spec.dt, ptr, length, base, st_t, inner, tma, 0, rowb))
+        if const_off:
+            base = f"{const_off}L + " + base
+        item = StagedItem(key, cls, spec.dt, ptr, length, base, st_t, inner, tma, 0, rowb)
+        if tma and self.tensor_tma and length <= 256 and self.D <= 256 and (const_off * e) % 16 == 0:
+            # one 4-D box (vector, head, D timesteps, batch) per chunk instead of one bulk copy per timestep
+            ext = lambda d: spec.shape[d] if spec.shape[d] > 1 else 1
+            pad = max(16, (ext(dims["v"]) * e + 15) // 16 * 16)
+            stb = lambda d: spec.st(d) * e if spec.st(d) else pad
+            item.tmap = {
+                "src": ptr, "off_bytes": const_off * e, "elt": e,
+                "dims": [ext(dims["v"]), ext(dims["h"]), ext(dims["t"]), ext(dims["b"])],
+                "strides_bytes": [stb(dims["h"]), stb(dims["t"]), stb(dims["b"])],
+                "box": [length, 1, self.D, 1],
+                "coord": ["m0" if cls == M1 else "0", "h" if spec.st(dims["h"]) else "0", None,
+                          "b" if spec.st(dims["b"]) else "0"],
+            }
+        self.items.append(item)
 
     def plan(self, graphs: Sequence[StepGraph], outputs_needed: Sequence[str] = ()) -> List[StepGraph]:
         """Lay out the raw ring, decide what is hoisted into the work buffer and
@@ -518,6 +538,14 @@ class KernelBuilder:
         self.tma_items = [i for i in self.items if i.tma]
         self.plain_items = [i for i in self.items if not i.tma]
         self.item_by_key = {i.key: i for i in self.items}
+        self.tmaps: List[dict] = []
+        for k, it in enumerate(i for i in self.tma_items if i.tmap):
+            it.tmap["name"] = f"tm{k}"
+            it.tmap["param_index"] = len(self.params)
+            it.tmap["src_index"] = self.params.index(it.tmap["src"])
+            self.params.append(f"tm{k}")
+            self.param_decl.append(f"FRNN_TMAP_PARAM tm{k}")
+            self.tmaps.append(it.tmap)
 
         avail: Dict[str, Shape] = {i.key: i.cls for i in self.items}
         for nm in self.const_scalars:
@@ -567,23 +595,35 @@ class KernelBuilder:
         w("(void)row0; (void)cb; (void)m0; (void)h; (void)b; (void)warp;")
 
     def emit_tma_issue(self, fn: str):
-        """Device function issuing the bulk copies of one chunk (warp 0 calls)."""
+        """Device function issuing the TMA copies of one chunk (warp 0 calls):
+        one tiled tensor-map load per item where a map exists, else one 1-D
+        bulk copy per item and timestep."""
         w = self.w
-        n = len(self.tma_items)
-        bytes_per_step = sum(i.length * ELT[i.dt] for i in self.tma_items)
-        w(f"// bulk copies of one chunk: {n} vectors per timestep, {bytes_per_step} bytes per timestep")
-        uniq = self._uniq_ptr_items(self.tma_items)
-        self.tma_issue_args = ", ".join(f"const void* {i.ptr}" for i in uniq)
-        self.tma_issue_call = ", ".join(i.ptr for i in uniq)
+        tens = [i for i in self.tma_items if i.tmap]
+        flat = [i for i in self.tma_items if not i.tmap]
+        n = len(flat)
+        flat_bytes = sum(i.length * ELT[i.dt] for i in flat)
+        tens_bytes = sum(i.length * ELT[i.dt] * self.D for i in tens)
+        w(f"// TMA copies of one chunk: {len(tens)} tiled loads of {self.D} timesteps, "
+          f"{n} bulk copies per timestep")
+        uniq = self._uniq_ptr_items(flat)
+        args = [f"const void* {i.ptr}" for i in uniq] + [f"const frnn_tmap* {i.tmap['name']}" for i in tens]
+        self.tma_issue_call = ", ".join([i.ptr for i in uniq] + [f"&{i.tmap['name']}" for i in tens])
         w.open(f"FRNN_DEV void {fn}(unsigned char* stage, u64* bar, int t0, int nv, int lane, int b, int h, int m0"
-               + (", " + self.tma_issue_args if n else "") + ")")
+               + (", " + ", ".join(args) if args else "") + ")")
+        if self.tma_items:
+            w.open("if (lane == 0)")
+            w(f"frnn_mbar_expect_tx(bar, {tens_bytes}u + (u32)nv * {flat_bytes}u);")
+            for it in tens:
+                c = it.tmap["coord"]
+                w(f"frnn_tma_load_4d(stage + {it.off}, {it.tmap['name']}, {c[0]}, {c[1]}, t0, {c[3]}, bar);")
+            w.close()
         if n:
-            w(f"if (lane == 0) frnn_mbar_expect_tx(bar, (u32)nv * {bytes_per_step}u);")
             w("frnn_warp_sync();")
             w.open(f"for (int i = lane; i < nv * {n}; i += 32)")
             w(f"const int k = i % {n}, tl = i / {n};")
             w.open("switch (k)")
-            for k, it in enumerate(self.tma_items):
+            for k, it in enumerate(flat):
                 e = ELT[it.dt]
                 w(f"case {k}: frnn_bulk_g2s(stage + {it.off} + tl * {it.rowb}, "
                   f"(const unsigned char*){it.ptr} + ({it.base} + (long)(t0 + tl) * {it.stride_t}L) * {e}, "
@@ -978,7 +1018,8 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     w.close()
     return KernelSource(kname, w.text(), (p.M // t.MB, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "tma_items": len(kb.tma_items),
-                         "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted]})
+                         "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted]},
+                        kb.tmaps)
 
 
 # ---------------------------------------------------------------------------
@@ -1079,8 +1120,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     ashape = (max(1, p.naux), p.B, p.H, p.T, p.M)
     for a, an in enumerate(aux_names):
         sp_a = TensorSpec(ashape[1:], _contig(ashape)[1:], DT_F32)
-        kb.add_item(an, M1, sp_a, "aux", {"b": 0, "h": 1, "t": 2, "v": 3})
-        kb.items[-1].base = f"{a * p.B * p.H * p.T * p.M}L + " + kb.items[-1].base
+        kb.add_item(an, M1, sp_a, "aux", {"b": 0, "h": 1, "t": 2, "v": 3}, const_off=a * p.B * p.H * p.T * p.M)
     yshape = (p.B, p.T, p.H, p.M)
     for j in range(n_out):
         if dy_used[j]:
@@ -1518,4 +1558,4 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
-                         "reverse": rev, "hoisted": [n.name for n in kb.hoisted]})
+                         "reverse": rev, "hoisted": [n.name for n in kb.hoisted]}, kb.tmaps)

@@ -19,7 +19,7 @@ LIB_PATH = os.path.join(HERE, "libfrnn_b200.so")
 
 SYMBOLS = ["frnn_abi_version", "frnn_last_error", "frnn_compile", "frnn_free", "frnn_module_load",
            "frnn_module_unload", "frnn_launch", "frnn_kernel_attrs", "frnn_l2_flush", "frnn_fp32_peak_probe",
-           "frnn_launch_static_scratch", "frnn_static_scratch_capacity"]
+           "frnn_launch_static_scratch", "frnn_static_scratch_capacity", "frnn_tensor_map_encode"]
 
 
 class FrnnError(RuntimeError):
@@ -55,6 +55,8 @@ def lib() -> ctypes.CDLL:
         L.frnn_launch_static_scratch.argtypes = [vp, ci, ctypes.POINTER(cu), ctypes.POINTER(cu), cu, vp,
                                                  ctypes.POINTER(vp), ci, ctypes.POINTER(ci), ctypes.POINTER(sz), ci]
         L.frnn_static_scratch_capacity.restype = sz
+        L.frnn_tensor_map_encode.argtypes = [vp, vp, cu, cu, ctypes.POINTER(ctypes.c_uint64),
+                                             ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint32)]
         L.frnn_l2_flush.argtypes = [vp, sz, vp]
         L.frnn_fp32_peak_probe.argtypes = [vp, ci, vp, ctypes.POINTER(ctypes.c_double)]
         _lib = L
@@ -103,6 +105,27 @@ def compile_cubin(src: str, opts: Sequence[str] = ()) -> Tuple[bytes, str]:
     return data, logtxt
 
 
+class StructArg:
+    """A by-value kernel parameter of 128 bytes, 64-byte aligned (a TMA tensor map)."""
+
+    def __init__(self):
+        self._raw = ctypes.create_string_buffer(256)
+        self.addr = (ctypes.addressof(self._raw) + 63) // 64 * 64
+
+
+def encode_tensor_map(base_ptr: int, elt_bytes: int, dims: Sequence[int], strides_bytes: Sequence[int],
+                      box: Sequence[int]) -> StructArg:
+    """Tensor map for a tiled TMA load (dims fastest first; strides for dims 1..)."""
+    arg = StructArg()
+    r = len(dims)
+    d = (ctypes.c_uint64 * r)(*[int(x) for x in dims])
+    st = (ctypes.c_uint64 * max(1, r - 1))(*[int(x) for x in strides_bytes])
+    bx = (ctypes.c_uint32 * r)(*[int(x) for x in box])
+    _check(lib().frnn_tensor_map_encode(ctypes.c_void_p(arg.addr), ctypes.c_void_p(int(base_ptr)), int(elt_bytes), r, d, st, bx),
+           "frnn_tensor_map_encode")
+    return arg
+
+
 class Module:
     """A loaded cubin with its kernels, bound to the device current at load."""
 
@@ -118,10 +141,14 @@ class Module:
         self._h = h
 
     def launch(self, kernel: int, grid: Sequence[int], block: int, smem: int, stream: int, ptrs: Sequence[int]):
-        """Launch with device pointers ``ptrs`` (ints) as the kernel parameters."""
+        """Launch with the kernel parameters ``ptrs``: ints are device pointers
+        (or integers of at most 8 bytes), :class:`StructArg` objects are
+        by-value struct parameters."""
         n = len(ptrs)
-        vals = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(p)) for p in ptrs])
-        args = (ctypes.c_void_p * n)(*[ctypes.addressof(vals) + i * ctypes.sizeof(ctypes.c_void_p) for i in range(n)])
+        vals = (ctypes.c_void_p * n)(*[ctypes.c_void_p(0 if isinstance(p, StructArg) else int(p)) for p in ptrs])
+        args = (ctypes.c_void_p * n)(*[p.addr if isinstance(p, StructArg) else
+                                       ctypes.addressof(vals) + i * ctypes.sizeof(ctypes.c_void_p)
+                                       for i, p in enumerate(ptrs)])
         g = (ctypes.c_uint * 3)(*[int(x) for x in grid])
         b = (ctypes.c_uint * 3)(int(block), 1, 1)
         _check(lib().frnn_launch(self._h, kernel, g, b, int(smem), ctypes.c_void_p(int(stream)), args, n),
@@ -134,8 +161,10 @@ class Module:
         pointed at the library's static scratch array; the entries of ``ptrs``
         at those indices are ignored.  Fails if the sizes exceed the array."""
         n = len(ptrs)
-        vals = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(p)) for p in ptrs])
-        args = (ctypes.c_void_p * n)(*[ctypes.addressof(vals) + i * ctypes.sizeof(ctypes.c_void_p) for i in range(n)])
+        vals = (ctypes.c_void_p * n)(*[ctypes.c_void_p(0 if isinstance(p, StructArg) else int(p)) for p in ptrs])
+        args = (ctypes.c_void_p * n)(*[p.addr if isinstance(p, StructArg) else
+                                       ctypes.addressof(vals) + i * ctypes.sizeof(ctypes.c_void_p)
+                                       for i, p in enumerate(ptrs)])
         g = (ctypes.c_uint * 3)(*[int(x) for x in grid])
         b = (ctypes.c_uint * 3)(int(block), 1, 1)
         idx = sorted(scratch)

@@ -341,6 +341,22 @@ class _CudaLauncher:
         self.rt, self.ks = runtime, ks
         self.mods: Dict[int, object] = {}
         self.log = ""
+        self._maps: Dict[tuple, object] = {}     # (device, map name, base address) -> encoded tensor map
+
+    def _tensor_maps(self, ptrs, idx):
+        """Tensor maps of this launch (they embed the tensors' base addresses)."""
+        out = []
+        for tm in self.ks.tmaps:
+            base = int(ptrs[tm["src_index"]]) + tm["off_bytes"]
+            key = (idx, tm["name"], base)
+            arg = self._maps.get(key)
+            if arg is None:
+                if len(self._maps) > 256:
+                    self._maps.clear()
+                arg = self.rt.encode_tensor_map(base, tm["elt"], tm["dims"], tm["strides_bytes"], tm["box"])
+                self._maps[key] = arg
+            out.append(arg)
+        return out
 
     def __call__(self, ptrs, device: th.device):
         idx = device.index if device.index is not None else th.cuda.current_device()
@@ -348,6 +364,7 @@ class _CudaLauncher:
             if idx not in self.mods:
                 cubin, self.log = self.rt.compile_cubin(self.ks.source)
                 self.mods[idx] = self.rt.Module(cubin, [self.ks.name], [self.ks.smem_bytes])
+            ptrs = list(ptrs) + self._tensor_maps(ptrs, idx)
             self.mods[idx].launch(0, self.ks.grid, self.ks.block, self.ks.smem_bytes,
                                   th.cuda.current_stream(idx).cuda_stream, ptrs)
 

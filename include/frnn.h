@@ -81,6 +81,20 @@ int frnn_module_unload(frnn_module_t m);
 int frnn_launch(frnn_module_t m, int kernel, const unsigned grid[3], const unsigned block[3],
                 unsigned smem_bytes, void* stream, void* const* args, int nargs);
 
+/*
+ * Encode a TMA tensor map (a 128-byte opaque descriptor, 64-byte aligned, in
+ * host memory at `out_map`) for a tiled `cp.async.bulk.tensor` load from the
+ * tensor at device address `base`: `rank` dimensions (1..5, fastest first) of
+ * `dims[i]` elements of `elt_bytes` bytes, byte strides `strides_bytes[i]` for
+ * dimensions 1..rank-1 (multiples of 16), and a box of `box[i]` elements.
+ * The generated kernels take such maps as `__grid_constant__` parameters: pass
+ * the address of the 128 bytes as that parameter's entry of `args`.  (No
+ * counterpart in the reference, whose kernels use scalar global loads,
+ * to_cuda.py:148-170.)  Out-of-range parts of a box read as zero.
+ */
+int frnn_tensor_map_encode(void* out_map, const void* base, unsigned elt_bytes, unsigned rank,
+                           const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
+
 /* Registers per thread, static shared bytes and local (spill) bytes per thread
  * of a loaded kernel, as the driver reports them. */
 int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, int* local_bytes);

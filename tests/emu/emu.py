@@ -19,6 +19,9 @@ _CACHE = os.path.join(tempfile.gettempdir(), "frnn_emu_cache")
 def _wrapper(ks) -> str:
     casts = []
     for i, d in enumerate(ks.param_decl):
+        if d.startswith("FRNN_TMAP_PARAM"):
+            casts.append(f"*(const frnn_tmap*)args[{i}]")
+            continue
         ctype = d.rsplit(" ", 1)[0].replace("__restrict__", "")
         casts.append(f"({ctype})args[{i}]")
     return (f'\nextern "C" void emu_run_{ks.name}(const unsigned* grid, unsigned nthreads, unsigned smem, void** args) {{\n'
@@ -54,6 +57,16 @@ class EmuLauncher:
         self.fn.restype = None
 
     def __call__(self, ptrs, device=None):
+        ptrs = list(ptrs)
+        keep = []
+        for tm in self.ks.tmaps:      # emulated tensor maps (layout of frnn_tmap in frnn_emu.h)
+            raw = ctypes.create_string_buffer(256)
+            addr = (ctypes.addressof(raw) + 63) // 64 * 64
+            vals = [int(ptrs[tm["src_index"]]) + tm["off_bytes"]] + list(tm["dims"]) + list(tm["strides_bytes"])
+            ctypes.memmove(addr, (ctypes.c_uint64 * 8)(*vals), 64)
+            ctypes.memmove(addr + 64, (ctypes.c_uint32 * 5)(*(list(tm["box"]) + [tm["elt"]])), 20)
+            keep.append(raw)
+            ptrs.append(addr)
         n = len(ptrs)
         args = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(p)) for p in ptrs])
         grid = (ctypes.c_uint * 3)(*self.ks.grid)

@@ -12,6 +12,8 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <cstdio>
+#include <cstdlib>
 #include <algorithm>
 #include <mutex>
 #include <thread>
@@ -83,6 +85,31 @@ FRNN_DEV void frnn_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
     std::lock_guard<std::mutex> g(emu_ctx->mtx);
     emu_mbar* b = (emu_mbar*)bar;
     b->pending -= (int)bytes; emu_mbar_settle(b);
+}
+// tensor map emulation: the test launcher fills this layout (128 bytes like the real descriptor)
+struct alignas(64) frnn_tmap {
+    unsigned char* base; u64 dims[4]; u64 strides[3]; u32 box[4]; u32 elt; u32 pad[9];
+};
+static_assert(sizeof(frnn_tmap) == 128, "tensor map emulation must be 128 bytes");
+#define FRNN_TMAP_PARAM const frnn_tmap
+FRNN_DEV void frnn_tma_load_4d(void* dst, const frnn_tmap* m, int c0, int c1, int c2, int c3, u64* bar) {
+    if (((uintptr_t)dst & 15) || ((long)c0 * m->elt) % 16) { fprintf(stderr, "emu: misaligned tensor load\n"); abort(); }
+    unsigned char* d = (unsigned char*)dst;
+    size_t total = 0;
+    for (u32 w3 = 0; w3 < m->box[3]; w3++)
+        for (u32 w2 = 0; w2 < m->box[2]; w2++)
+            for (u32 w1 = 0; w1 < m->box[1]; w1++)
+                for (u32 w0 = 0; w0 < m->box[0]; w0++) {
+                    long i0 = c0 + w0, i1 = c1 + w1, i2 = c2 + w2, i3 = c3 + w3;
+                    bool in = i0 >= 0 && i1 >= 0 && i2 >= 0 && i3 >= 0 && (u64)i0 < m->dims[0] && (u64)i1 < m->dims[1] &&
+                              (u64)i2 < m->dims[2] && (u64)i3 < m->dims[3];
+                    if (in) memcpy(d, m->base + i0 * m->elt + i1 * m->strides[0] + i2 * m->strides[1] + i3 * m->strides[2], m->elt);
+                    else memset(d, 0, m->elt);
+                    d += m->elt; total += m->elt;
+                }
+    std::lock_guard<std::mutex> g(emu_ctx->mtx);
+    emu_mbar* b = (emu_mbar*)bar;
+    b->pending -= (int)total; emu_mbar_settle(b);
 }
 FRNN_DEV bool frnn_mbar_try(u64* bar, u32 parity) {
     std::lock_guard<std::mutex> g(emu_ctx->mtx);

@@ -40,6 +40,11 @@ def test_static_scratch_matches_caller_allocated_scratch():
         err = torch.zeros(1, dtype=torch.int32, device=DEV)
         used = plan.g_fw.used_inputs()
 
+        def tensor_maps(ptrs):
+            # the kernel's TMA tensor maps embed the input addresses: encode them for this call
+            return [runtime.encode_tensor_map(ptrs[tm["src_index"]] + tm["off_bytes"], tm["elt"], tm["dims"],
+                                              tm["strides_bytes"], tm["box"]) for tm in fw.tmaps]
+
         def run(inputs, static):
             y = torch.full((B, T, H, M), float("nan"), device=DEV)
             ST = torch.full((B, H, M, N), float("nan"), device=DEV)
@@ -48,6 +53,7 @@ def test_static_scratch_matches_caller_allocated_scratch():
             ptrs = [x.data_ptr() for x, u in zip(inputs[:-1], used) if u]
             ptrs += [inputs[-1].data_ptr(), y.data_ptr(), ST.data_ptr()]
             ptrs += [0 if static else ck.data_ptr(), 0 if static else aux.data_ptr(), err.data_ptr()]
+            ptrs += tensor_maps(ptrs)
             assert len(ptrs) == len(fw.params)
             if static:
                 mod.launch_static_scratch(0, fw.grid, fw.block, fw.smem_bytes, stream, ptrs,
@@ -70,6 +76,7 @@ def test_static_scratch_matches_caller_allocated_scratch():
         cap = runtime.lib().frnn_static_scratch_capacity()
         assert cap == 32 << 20
         ptrs = [x.data_ptr() for x, u in zip(xs[:-1], used) if u] + [xs[-1].data_ptr(), 0, 0, 0, 0, err.data_ptr()]
+        ptrs += tensor_maps(ptrs)
         with pytest.raises(runtime.FrnnError, match="more scratch than the library's static buffer"):
             mod.launch_static_scratch(0, fw.grid, fw.block, fw.smem_bytes, stream, ptrs, {i_ck: cap, i_aux: 4096})
         mod.close()
