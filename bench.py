@@ -87,6 +87,10 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def bytes_io(tensors):
+    return sum(t.numel() * t.element_size() for t in tensors)
+
+
 def cpu_sample(opname, B, T, H, M, N, seconds_hint=15.0):
     """Times the CPU oracle (fwd + autograd bwd) on a (b,h) sub-slice of the
     workload and scales to whole-workload tokens/s (the slices are independent
@@ -275,6 +279,8 @@ def main():
     if rank == 0:
         plan = op.forward_func.plan
         fw_src, bw_src = op.forward_func.sources
+        stream_mb = (bytes_io(xs) * 3 + 2 * B * T * H * M * 2 + plan.nck * B * H * M * N * 4 * 2
+                     + len(plan.aux) * B * T * H * M * 4 * 2) / 1e6
         k_bw = plan.k_joint - plan.k_fwd
         elems = B * T * H * M * N
         bw_avg, fw_avg = statistics.mean(bw_ms), statistics.mean(fw_ms)
@@ -297,9 +303,12 @@ def main():
             "dtype": "fp32", "data": "synthetic",
             "config": {"workload": f"{args.op} fwd+bwd, B{B} T{T} H{H} {M}x{N} per GPU, bf16 I/O, fp32 state and math",
                        "io_dtype": "bf16", "global_batch": B * world, "seq_len": T, "parallelism": f"batch shards x{world}, no collective",
-                       "l2": "no flush: each step streams >2 GB of inputs, checkpoints and row sums (L2 is 126 MB)",
-                       "checkpoint_every": plan.D, "fw_tile": [plan.fw_tile.R, plan.fw_tile.C, plan.fw_tile.MB],
-                       "bw_tile": [plan.bw_tile.R, plan.bw_tile.C]},
+                       "l2": f"no flush: each step streams {stream_mb:.0f} MB of inputs, outputs, checkpoints and row sums "
+                             "through HBM (L2 is 126 MB)",
+                       "checkpoint_every": plan.D, "backward": "reverse re-step" if plan.reverse else "recompute from slots",
+                       "fw_kernel": {"grid": list(fw_src.grid), "block": fw_src.block, "smem": fw_src.smem_bytes},
+                       "bw_kernel": {"grid": list(bw_src.grid), "block": bw_src.block, "smem": bw_src.smem_bytes,
+                                     "tile": [plan.bw_tile.R, plan.bw_tile.C]}},
             "fw_ms": fw_avg, "bw_ms": bw_avg,
             "roofline_fraction_step": max(t_fp32, t_hbm) / (ms_per_step * 1e-3),
             "roofline": {"bound": "fp32", "kernel": bw_src.name, "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",

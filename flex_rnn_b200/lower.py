@@ -894,7 +894,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     (g2,) = kb.plan([g])
     stage_bytes = kb.stage_bytes
     BAR_BYTES = 128
-    off_wk = BAR_BYTES + 2 * stage_bytes
+    off_wk = BAR_BYTES + stage_bytes      # one raw buffer: it is free again as soon as a chunk is converted
     smem_bytes = off_wk + kb.wk_bytes
     nchunk = (p.T + dstage - 1) // dstage
     nck = (p.T + dck - 1) // dck
@@ -925,8 +925,6 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     if has_tma:
         w.open("if (warp == 0)")
         w(f"fw_issue(stage, &full[0], 0, min({dstage}, {p.T}), lane, b, h, m0{tma_call});")
-        if nchunk > 1:
-            w(f"fw_issue(stage + {stage_bytes}, &full[1], {dstage}, min({dstage}, {p.T - dstage}), lane, b, h, m0{tma_call});")
         w.close()
 
     body = Body(w, t, g2.shape)
@@ -940,8 +938,8 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
 
     w("#pragma unroll 1")
     w.open(f"for (int c = 0; c < {nchunk}; c++)")
-    w(f"const int buf = c & 1, t0 = c * {dstage}, nv = min({dstage}, {p.T} - t0);")
-    w(f"unsigned char* sp = stage + buf * {stage_bytes};")
+    w(f"const int t0 = c * {dstage}, nv = min({dstage}, {p.T} - t0);")
+    w("unsigned char* sp = stage;")
     if kb.plain_items:
         w(f"if (c + 1 < {nchunk}) {{")
         w.ind += 1
@@ -949,19 +947,13 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         w.ind -= 1
         w("}")
     if has_tma:
-        w(f"if (!frnn_mbar_wait(&full[buf], (c >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+        w(f"if (!frnn_mbar_wait(&full[0], c & 1, err, {ERR_STAGE_TIMEOUT})) return;")
     w("frnn_block_sync();   // previous chunk's work buffer is no longer read; plain stores are visible")
     kb.emit_convert("sp", "wk", "nv")
-    if kb.plain_items:
-        w(f"if (c + 1 < {nchunk}) {{")
-        w.ind += 1
-        kb.emit_plain_store(f"(stage + (buf ^ 1) * {stage_bytes})")
-        w.ind -= 1
-        w("}")
     w("frnn_block_sync();   // work buffer complete; the raw buffer may be refilled")
     if has_tma:
-        w.open(f"if (warp == 0 && c + 2 < {nchunk})")
-        w(f"fw_issue(sp, &full[buf], t0 + {2 * dstage}, min({dstage}, {p.T} - t0 - {2 * dstage}), lane, b, h, m0{tma_call});")
+        w.open(f"if (warp == 0 && c + 1 < {nchunk})")
+        w(f"fw_issue(sp, &full[0], t0 + {dstage}, min({dstage}, {p.T} - t0 - {dstage}), lane, b, h, m0{tma_call});")
         w.close()
     sub_len = math.gcd(dstage, dck)
     w("#pragma unroll 1")
@@ -1008,6 +1000,12 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     w.close()
     w.close()  # tl loop
     w.close()  # tl0 loop
+    if kb.plain_items:
+        w(f"if (c + 1 < {nchunk}) {{")
+        w.ind += 1
+        kb.emit_plain_store("stage")
+        w.ind -= 1
+        w("}")
     w.close()  # chunk loop
     for k in range(ns):
         kb.emit_tile_global(vname(p.st_names[k]), p.states[k], f"sT_{k}",
@@ -1144,7 +1142,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     ck_tma = (not rev) and use_tma and slot_bytes % 16 == 0
     BAR_BYTES = 128
     off_stage = BAR_BYTES
-    off_wk = off_stage + 2 * stage_bytes
+    off_wk = off_stage + stage_bytes       # one raw buffer (free again once a chunk is converted)
     off_slots = off_wk + kb.wk_bytes
     off_ring = off_slots + nphys * ns * slot_bytes
     smem_bytes = off_ring + ring_bytes
@@ -1199,8 +1197,6 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     if has_tma:
         w.open("if (warp == 0)")
         w(f"bw_issue(stage, &full[0], {first_c * D}, {nv_first}, lane, b, h, m0{tma_call});")
-        if nchunk > 1:
-            w(f"bw_issue(stage + {stage_bytes}, &full[1], {(first_c - 1) * D}, {D}, lane, b, h, m0{tma_call});")
         w.close()
     if not rev:
         ck_fetch(str(first_c), "0")
@@ -1436,8 +1432,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     # ------------------------------------------------------------------ chunk loop
     w("#pragma unroll 1")
     w.open(f"for (int c = 0; c < {nchunk}; c++)")
-    w(f"const int kc = {nchunk - 1} - c, t0 = kc * {D}, nv = min({D}, {p.T} - t0), buf = c & 1;")
-    w(f"unsigned char* sp = stage + buf * {stage_bytes};")
+    w(f"const int kc = {nchunk - 1} - c, t0 = kc * {D}, nv = min({D}, {p.T} - t0);")
+    w("unsigned char* sp = stage;")
     if kb.plain_items:
         w("if (kc > 0) {")
         w.ind += 1
@@ -1445,19 +1441,13 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.ind -= 1
         w("}")
     if has_tma:
-        w(f"if (!frnn_mbar_wait(&full[buf], (c >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
-    w("frnn_block_sync();   // previous chunk's work buffer is no longer read")
+        w(f"if (!frnn_mbar_wait(&full[0], c & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+    w("frnn_block_sync();   // previous chunk's work buffer is no longer read; plain stores are visible")
     kb.emit_convert("sp", "wk", "nv")
-    if kb.plain_items:
-        w("if (kc > 0) {")
-        w.ind += 1
-        kb.emit_plain_store(f"(stage + (buf ^ 1) * {stage_bytes})")
-        w.ind -= 1
-        w("}")
     w("frnn_block_sync();   // work buffer complete; the raw buffer may be refilled")
     if has_tma:
-        w.open("if (warp == 0 && kc >= 2)")
-        w(f"bw_issue(sp, &full[buf], (kc - 2) * {D}, {D}, lane, b, h, m0{tma_call});")
+        w.open("if (warp == 0 && kc >= 1)")
+        w(f"bw_issue(sp, &full[0], (kc - 1) * {D}, {D}, lane, b, h, m0{tma_call});")
         w.close()
 
     if rev:
@@ -1532,6 +1522,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if redw and kflush > 1:
             emit_flush()
         w("#undef PHYS")
+    if kb.plain_items:
+        w("if (kc > 0) {")
+        w.ind += 1
+        kb.emit_plain_store("stage")
+        w.ind -= 1
+        w("}")
     w.close()   # chunk loop
 
     for k in range(ns):

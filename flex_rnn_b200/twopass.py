@@ -78,7 +78,7 @@ class Tuning:
     """Code-generation parameters (defaults picked by ``default_tuning``)."""
     fw_r: int = 4            # forward tile: rows x columns per thread, rows per CTA
     fw_c: int = 32
-    fw_mb: int = 32
+    fw_mb: int = 128
     fw_stage: int = 16       # timesteps per staged chunk (forward)
     fw_min_blocks: int = 1
     bw_r: int = 8            # backward tile
@@ -87,10 +87,12 @@ class Tuning:
     nslots: int = 2
     kflush: int = 8          # steps of gradient partials reduced together (lowered until shared memory fits)
     reverse: int = 1         # use the reverse re-step when the state update is additive
-    rev_stage: int = 8       # reverse mode: timesteps per staged chunk
+    rev_stage: int = 16      # reverse mode: timesteps per staged chunk
     rev_resync: int = 4      # reverse mode: chunks between exact checkpoints
-    fw_unroll: int = 2       # unroll factor of the timestep loops
-    bw_unroll: int = 2
+    fw_unroll: int = 4       # unroll factor of the timestep loops
+    bw_unroll: int = 4
+    slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
+    autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     use_tma: bool = True
 
 
@@ -258,8 +260,17 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
 
     # pick the backward's staging / flush parameters that fit shared memory
     choice = None
-    seg0 = tu.rev_stage if reverse is not None else tu.seg
-    for sg in range(seg0, 0, -1):
+    import dataclasses
+    tu = dataclasses.replace(tu)
+    if reverse is not None:
+        pairs = [(sg, tu.nslots) for sg in range(tu.rev_stage, 0, -1)]
+    else:
+        # (steps per segment, slots): fewer recomputed steps first, then what the tuning asks for
+        pairs = ([(2, 4)] if tu.slot_search and T >= 8 else []) + [(sg, tu.nslots) for sg in range(tu.seg, 0, -1)]
+        if tu.nslots > 1:
+            pairs += [(sg, 1) for sg in range(tu.seg, 0, -1)]
+    ks = None
+    for sg, nsl in pairs:
         k = max(1, tu.kflush)
         cands = []
         while k >= 1:
@@ -267,7 +278,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             k //= 2
         for kflush, bufs in cands:
             try:
-                ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, tu.nslots,
+                ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
                                    tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
             except lower.LoweringError:
                 if any(g.cls == MN for g in grads):
@@ -276,9 +287,11 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
                 raise
             if ks.smem_bytes <= SMEM_LIMIT:
                 choice = (sg, kflush, bufs)
+                tu.nslots = nsl
                 break
         if choice or ks is None:
             break
+    seg0 = pairs[0][0]
     if choice is None:
         if any(g.cls == MN for g in grads):
             choice = (seg0, 1, 1)
@@ -306,29 +319,53 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     return plan, fw_meta, bw_meta
 
 
-def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
-    """Emit the CUDA source of the forward and the backward kernel."""
+def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None) -> lower.KernelSource:
+    """Emit the forward kernel (for ``tile`` instead of the planned tile if given)."""
     p, tu = plan.problem, plan.tuning
-    rev = plan.reverse
-    # forward: keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
+    tile = tile or plan.fw_tile
+    # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
     stage = tu.fw_stage
     while True:
-        fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, plan.fw_tile, stage, plan.D, tu.use_tma,
-                          tu.fw_min_blocks, prelude(), final_ckpt=rev is not None, step_unroll=tu.fw_unroll)
+        fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, tile, stage, plan.D, tu.use_tma,
+                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None, step_unroll=tu.fw_unroll)
         ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
         per_sm = min(max(1, -(-ncta // 148)), 2048 // fw.block, 32)
         if stage <= 4 or fw.smem_bytes * per_sm <= 200 * 1024:
             break
         stage //= 2
+    if fw.smem_bytes > SMEM_LIMIT:
+        raise lower.LoweringError(f"kernel {fw.name} needs {fw.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
+    return fw
+
+
+def forward_tile_candidates(plan: Plan) -> List[lower.Tile]:
+    """Alternative forward tilings worth timing (the planned one first)."""
+    p = plan.problem
+    out, seen = [plan.fw_tile], {(plan.fw_tile.R, plan.fw_tile.C, plan.fw_tile.MB)}
+    for r, c in ((2, 64), (4, 32), (8, 16)):
+        try:
+            t = choose_tile(p.M, p.N, r, c, plan.tuning.fw_mb)
+        except lower.LoweringError:
+            continue
+        if (t.R, t.C, t.MB) not in seen and t.R * t.C * plan.n_st <= 128:
+            seen.add((t.R, t.C, t.MB))
+            out.append(t)
+    return out
+
+
+def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
+    """Emit the CUDA source of the forward and the backward kernel."""
+    p, tu = plan.problem, plan.tuning
+    rev = plan.reverse
+    fw = generate_forward(plan)
     if any(g.cls == MN for g in plan.grads):
         raise lower.LoweringError("matrix-per-head inputs are not supported yet")
     sg, kflush, bufs = plan.bw_choice
     bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
                        plan.dnext_names, plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),          # type: ignore[attr-defined]
                        kflush=kflush, ring_bufs=bufs, reverse=rev, step_unroll=tu.bw_unroll)
-    for kk in (fw, bw):
-        if kk.smem_bytes > SMEM_LIMIT:
-            raise lower.LoweringError(f"kernel {kk.name} needs {kk.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
+    if bw.smem_bytes > SMEM_LIMIT:
+        raise lower.LoweringError(f"kernel {bw.name} needs {bw.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
     return fw, bw
 
 
@@ -425,6 +462,35 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             assert (t.data_ptr() % 16 == 0) or not f, (
                 f"{what} #{i + 1} was 16-byte aligned at compilation but is not now")
 
+    tuned = {"fw": _launcher is not None or not plan.tuning.autotune, "launch_fw": launch_fw, "fw_src": fw_src}
+
+    def autotune_forward(ptrs, device):
+        """Time the alternative forward tilings once on the real arguments (the
+        forward kernel only writes its outputs) and keep the fastest."""
+        tuned["fw"] = True
+        best = None
+        for tile in forward_tile_candidates(plan):
+            try:
+                ks = fw_src if tile is plan.fw_tile else generate_forward(plan, tile)
+                launcher = launch_fw if tile is plan.fw_tile else make(ks)
+                launcher(ptrs, device)                                   # compile + warm up
+                ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
+                ev[0].record()
+                for _ in range(2):
+                    launcher(ptrs, device)
+                ev[1].record()
+                ev[1].synchronize()
+                ms = ev[0].elapsed_time(ev[1]) / 2
+            except (lower.LoweringError, RuntimeError):
+                continue
+            if "spill stores" in getattr(launcher, "log", "") and " 0 bytes spill stores" not in launcher.log:
+                ms *= 1.0    # spilling variants compete on time like the others
+            if best is None or ms < best[0]:
+                best = (ms, launcher, ks)
+        if best is not None:
+            tuned["launch_fw"], tuned["fw_src"] = best[1], best[2]
+            forward.sources = (best[2], bw_src)       # type: ignore[attr-defined]
+
     def forward(inputs_, state0):
         verify_meta(inputs_, in_meta, "input Tensor metadata doesn't match compilation\n")
         verify_meta(state0, st_meta, "initial state Tensor metadata doesn't match compilation\n")
@@ -441,7 +507,9 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             ptrs = [x.data_ptr() for x, u in zip(inputs_, fw_used[:nin]) if u]
             ptrs += [s.data_ptr() for s in state0] + [o.data_ptr() for o in outs] + [s.data_ptr() for s in stT]
             ptrs += [s.data_ptr() for s in store] + [aux.data_ptr(), ew.data_ptr()]
-            launch_fw(ptrs, device)
+            if not tuned["fw"]:
+                autotune_forward(ptrs, device)
+            tuned["launch_fw"](ptrs, device)
         return (*outs, *stT, *store, aux)
 
     def backward(doutput, dstateT, inputs_, state_store, aux_):
