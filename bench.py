@@ -42,6 +42,9 @@ WORKLOADS = {
     "mamba2": ("mamba2", 8, 1024, 32, 64, 128),
     "gated_delta_rule": ("gated_delta_rule", 8, 1024, 32, 128, 128),
 }
+# DRAM bytes (read + write) of one backward launch per (batch, head) pair, from the ncu capture summarised in
+# profiles/delta_rule_b2_frnn_fw_bw_ncu_full.md (B=2: 202.9 MB over 64 pairs); traffic grows with the pair count
+NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 202.9e6 / 64}
 METRIC = "fwd+bwd tokens/s"
 UNIT = "tokens/s"
 
@@ -312,7 +315,9 @@ def main():
             "fw_ms": fw_avg, "bw_ms": bw_avg,
             "roofline_fraction_step": max(t_fp32, t_hbm) / (ms_per_step * 1e-3),
             "roofline": {"bound": "fp32", "kernel": bw_src.name, "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",
-                         "frac": achieved / fp32_peak, "traffic": None,
+                         "frac": achieved / fp32_peak,
+                         "traffic": NCU_BW_DRAM_BYTES_PER_BH[args.op] * B * H if args.op in NCU_BW_DRAM_BYTES_PER_BH else None,
+                         "algorithmic_bytes": bytes_io(xs) * 2 + 2 * B * T * H * M * 2 + B * H * M * N * 2 - xs[-1].numel() * 2,
                          "peak_source": f"measured in this run by the FMA probe kernel ({sms} SMs); HBM copy peak {hbm} GB/s "
                                         + ("of measured" if peaks else "of fallback"),
                          "flops_per_launch": elems * k_bw, "k_joint": plan.k_joint, "k_fwd": plan.k_fwd,

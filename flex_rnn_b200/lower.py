@@ -1114,7 +1114,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         kb.add_param(f"dx{go.index}", "void", False)
     kb.add_param("err", "int", False)
 
-    const_inputs = _stage_inputs(kb, p, used, allow_mn=False)
+    const_inputs = _stage_inputs(kb, p, used, allow_mn=True)
     ashape = (max(1, p.naux), p.B, p.H, p.T, p.M)
     for a, an in enumerate(aux_names):
         sp_a = TensorSpec(ashape[1:], _contig(ashape)[1:], DT_F32)
@@ -1217,6 +1217,11 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w(f"float gacc{go.index}[{t.R}];")
             w("#pragma unroll")
             w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] = 0.0f;")
+        if go.cls == MN:
+            # matrix-per-head inputs are time-invariant: their gradient tile accumulates in registers
+            w(f"float gmat{go.index}[{t.R * t.C}];")
+            w("#pragma unroll")
+            w(f"for (int i = 0; i < {t.R * t.C}; i++) gmat{go.index}[i] = 0.0f;")
     # time-invariant per-column / per-head gradients: thread e accumulates element e over time
     tinv = [go for go in pm_vec + pm_sc if go.over_t]
     nred_per_thread = (redw + t.NT - 1) // t.NT if redw else 0
@@ -1402,6 +1407,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 kb.emit_row_vec_store(f"gv{go.index}", go.spec.dt, f"dx{go.index}", idx0, go.spec.st(3),
                                       go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)),
                                       atomic=go.atomic)
+        for go in grads:
+            if go.cls != MN:
+                continue
+            if sub.partial.get(go.value, False):
+                raise LoweringError("matrix gradient came out as a sum over rows")
+            sub.loops(MN, lambda r, c, go=go: f"gmat{go.index}[{r}*{t.C}+{c}] += {sub.at(go.value, r, c)};")
         if redw:
             w("if (rcnt == 0) rt_first = t;")
             w(f"float* rb = ring + (rhalf * {kflush} + rcnt) * {step_floats} + rg * {redw_pad};")
@@ -1537,6 +1548,9 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if go.over_t and go.cls == M1:
             idx0 = _elem_off(go.spec, [(0, "b"), (2, "h")])
             kb.emit_row_vec_store(f"gacc{go.index}", DT_F32, f"dx{go.index}", idx0, go.spec.st(3), False, atomic=True)
+        if go.cls == MN:
+            kb.emit_tile_global(f"gmat{go.index}", go.spec, f"dx{go.index}", _elem_off(go.spec, [(0, "b"), (2, "h")]),
+                                3, 4, load=False, add=True)
     if tinv:
         w("#pragma unroll")
         w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")

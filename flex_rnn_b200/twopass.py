@@ -217,8 +217,17 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             raise AssertionError("Only torch.sum(x, dim=-1, keepdim=True) is supported")
 
     tu = tuning or default_tuning(B, T, H, M, N, nst)
-    fw_tile = choose_tile(M, N, tu.fw_r, tu.fw_c, tu.fw_mb)
-    bw_tile = choose_tile(M, N, tu.bw_r, tu.bw_c, None)
+    # register budget: every state (and, in the backward, its gradient) and every matrix-per-head input
+    # (and its gradient) is an R x C tile per thread
+    n_mat = sum(1 for c in in_cls if c == MN)
+    fw_tiles, bw_tiles = nst + n_mat, 2 * nst + 2 * n_mat
+    fr, fc, br, bc = tu.fw_r, tu.fw_c, tu.bw_r, tu.bw_c
+    while fr * fc * fw_tiles > 160 and fr * fc > 4:
+        fr, fc = (fr // 2, fc) if fr >= 4 else (fr, max(1, fc // 2))
+    while br * bc * bw_tiles > 160 and br * bc > 4:
+        br, bc = (br // 2, bc) if br >= bc else (br, max(1, bc // 2))
+    fw_tile = choose_tile(M, N, fr, fc, tu.fw_mb)
+    bw_tile = choose_tile(M, N, br, bc, None)
     # additive state update S' = S +/- X with X free of the state (given the saved row sums):
     # the backward can step the state backwards instead of recomputing it from checkpoints
     reverse = None
@@ -277,14 +286,8 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             cands += [(k, 2), (k, 1)]
             k //= 2
         for kflush, bufs in cands:
-            try:
-                ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
-                                   tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
-            except lower.LoweringError:
-                if any(g.cls == MN for g in grads):
-                    ks = None
-                    break
-                raise
+            ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
+                               tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
             if ks.smem_bytes <= SMEM_LIMIT:
                 choice = (sg, kflush, bufs)
                 tu.nslots = nsl
@@ -293,10 +296,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             break
     seg0 = pairs[0][0]
     if choice is None:
-        if any(g.cls == MN for g in grads):
-            choice = (seg0, 1, 1)
-        else:
-            raise lower.LoweringError(f"the backward kernel of a {M}x{N} state does not fit shared memory")
+        raise lower.LoweringError(f"the backward kernel of a {M}x{N} state does not fit shared memory")
     if reverse is not None:
         D = choice[0] * reverse.resync
         nck = (T + D - 1) // D + 1          # plus the final state
@@ -358,8 +358,6 @@ def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
     p, tu = plan.problem, plan.tuning
     rev = plan.reverse
     fw = generate_forward(plan)
-    if any(g.cls == MN for g in plan.grads):
-        raise lower.LoweringError("matrix-per-head inputs are not supported yet")
     sg, kflush, bufs = plan.bw_choice
     bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
                        plan.dnext_names, plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),          # type: ignore[attr-defined]
