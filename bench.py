@@ -317,7 +317,7 @@ def main():
             "roofline": {"bound": "fp32", "kernel": bw_src.name, "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp32_peak,
                          "traffic": NCU_BW_DRAM_BYTES_PER_BH[args.op] * B * H if args.op in NCU_BW_DRAM_BYTES_PER_BH else None,
-                         "algorithmic_bytes": bytes_io(xs) * 2 + 2 * B * T * H * M * 2 + B * H * M * N * 2 - xs[-1].numel() * 2,
+                         "algorithmic_bytes": bytes_io(xs) * 2 + B * T * H * M * 2,
                          "peak_source": f"measured in this run by the FMA probe kernel ({sms} SMs); HBM copy peak {hbm} GB/s "
                                         + ("of measured" if peaks else "of fallback"),
                          "flops_per_launch": elems * k_bw, "k_joint": plan.k_joint, "k_fwd": plan.k_fwd,
