@@ -155,3 +155,26 @@ def test_full_size_slices_and_split():
     for i in range(n):
         assert O.rel_err(torch.cat([gall[i], gall[n + 1 + i]], 1), g1[i]) < 2e-5
     assert O.rel_err(gall[n], g1[n]) < 2e-5
+
+
+def test_check_grad_and_torch_compile():
+    """The user-facing check (compiled vs naive_fp64, tolerance 1e-2 as in the
+    reference's check_grad) and the same op under torch.compile without a
+    graph break."""
+    xs, _, _ = O.make_case("rwkv7", 2, 32, 2, 64, 64, torch.float32)
+    xs = [x.to(DEV) for x in xs]
+    op = flex_rnn_b200.jit(O.rwkv7)
+    err = flex_rnn_b200.check_grad(op, op.naive_fp64, xs, verbose=False)
+    assert err < 1e-4
+    compiled = torch.compile(lambda *z: op(*z), fullgraph=True)
+    y0, S0 = op(*xs)
+    y1, S1 = compiled(*xs)
+    assert torch.equal(y0, y1) and torch.equal(S0, S1)
+    leaves = [x.clone().requires_grad_() for x in xs]
+    y, S = compiled(*leaves)
+    g = torch.autograd.grad([y.sum(), S.sum()], leaves)
+    leaves2 = [x.clone().requires_grad_() for x in xs]
+    y2, S2 = op(*leaves2)
+    g2 = torch.autograd.grad([y2.sum(), S2.sum()], leaves2)
+    for a, b in zip(g, g2):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
