@@ -802,6 +802,39 @@ class KernelBuilder:
                     w(f"frnn_io<{spec.dt}>::st({ptr}, {idx}, {el});")
         w.close()
 
+    def emit_obuf_put(self, arr: str, obuf: str, row_expr: str, vidx: int, nvals: int):
+        """Lane 0 of each row group parks R per-row values of one timestep in the
+        shared output buffer (row ``row_expr``, value slot ``vidx``)."""
+        w, t = self.w, self.t
+        cnt = _pick_cnt(t.R, DT_F32, t.R)
+        w.open("if (l == 0)")
+        for q in range(t.R // cnt):
+            w(f"frnn_stv<0,{cnt}>({obuf}, ({row_expr}) * {nvals * t.MB} + {vidx * t.MB} + rg * {t.R} + {q * cnt}, &{arr}[{q * cnt}]);")
+        w.close()
+
+    def emit_obuf_flush(self, obuf: str, nrows: str, vidx: int, nvals: int, dt: int, ptr: str, idx_of_row, stride_m: int,
+                        aligned: bool):
+        """All threads: write ``nrows`` parked timesteps of value slot ``vidx`` to
+        global memory with wide stores.  ``idx_of_row(s)`` gives the element
+        offset of row m0 at parked row ``s``."""
+        w, t = self.w, self.t
+        vw = 8 if ELT[dt] == 2 else 4
+        while t.MB % vw:
+            vw //= 2
+        fast = stride_m == 1 and aligned
+        w.open(f"for (int it = tid; it < ({nrows}) * {t.MB // vw}; it += {t.NT})")
+        w(f"const int s = it / {t.MB // vw}, mm = (it % {t.MB // vw}) * {vw};")
+        w(f"float v[{vw}];")
+        cnt = min(4, vw)
+        for q in range(vw // cnt):
+            w(f"frnn_ldv<0,{cnt}>({obuf}, s * {nvals * t.MB} + {vidx * t.MB} + mm + {q * cnt}, &v[{q * cnt}]);")
+        if fast:
+            w(f"frnn_stv<{dt},{vw}>({ptr}, {idx_of_row('s')} + mm, v);")
+        else:
+            w("#pragma unroll")
+            w(f"for (int q = 0; q < {vw}; q++) frnn_io<{dt}>::st({ptr}, {idx_of_row('s')} + (long)(mm + q) * {stride_m}L, v[q]);")
+        w.close()
+
     def emit_row_vec_store(self, arr: str, dt: int, ptr: str, idx0: str, stride_m: int, aligned: bool,
                            atomic: bool = False):
         """Lane 0 of each row group stores R per-row values (rows row0..row0+R)."""
@@ -895,7 +928,10 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     stage_bytes = kb.stage_bytes
     BAR_BYTES = 128
     off_wk = BAR_BYTES + stage_bytes      # one raw buffer: it is free again as soon as a chunk is converted
-    smem_bytes = off_wk + kb.wk_bytes
+    n_ob = n_out + len(aux_names)         # per-row results parked in shared memory, written out once per chunk
+    off_ob = off_wk + kb.wk_bytes
+    ob_bytes = (dstage * n_ob * t.MB * 4 + 127) // 128 * 128
+    smem_bytes = off_ob + ob_bytes
     nchunk = (p.T + dstage - 1) // dstage
     nck = (p.T + dck - 1) // dck
     nck_store = nck + (1 if final_ckpt else 0)
@@ -911,6 +947,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     w("u64* full = (u64*)smem;")
     w(f"unsigned char* stage = smem + {BAR_BYTES};")
     w(f"float* wk = (float*)(smem + {off_wk});")
+    w(f"float* obuf = (float*)(smem + {off_ob});")
     has_tma = bool(kb.tma_items)
     if has_tma:
         w.open("if (tid == 0)")
@@ -982,24 +1019,31 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         w(f"float yv{j}[{t.R}];")
         w("#pragma unroll")
         w(f"for (int r = 0; r < {t.R}; r++) yv{j}[r] = {sub.at(o, 'r', '0')};")
-        kb.emit_row_vec_store(f"yv{j}", p.out_dt[j], f"out{j}",
-                              _elem_off(ys, [(0, "b"), (1, "t"), (2, "h")]), 1,
-                              (p.M * ELT[p.out_dt[j]]) % 16 == 0)
+        kb.emit_obuf_put(f"yv{j}", "obuf", "tl", j, n_ob)
     ashape = (max(1, p.naux), p.B, p.H, p.T, p.M)
     aspec = TensorSpec(ashape, _contig(ashape), DT_F32)
     for a, an in enumerate(aux_names):
         w(f"float av{a}[{t.R}];")
         w("#pragma unroll")
         w(f"for (int r = 0; r < {t.R}; r++) av{a}[r] = {sub.at(an, 'r', '0')};")
-        kb.emit_row_vec_store(f"av{a}", DT_F32, "aux",
-                              _elem_off(aspec, [(0, str(a)), (1, "b"), (2, "h"), (3, "t")]), 1,
-                              (p.M * 4) % 16 == 0)
+        kb.emit_obuf_put(f"av{a}", "obuf", "tl", n_out + a, n_ob)
     for k in range(ns):
         o = outs[n_out + k]
         sub.loops(stcls, lambda r, c, k=k, o=o: f"{body.at(p.st_names[k], r, c)} = {sub.at(o, r, c)};")
     w.close()
     w.close()  # tl loop
     w.close()  # tl0 loop
+    if n_ob:
+        w("frnn_block_sync();   // the chunk's outputs and row sums are parked in shared memory")
+        for j in range(n_out):
+            ys = TensorSpec(yspec_shape, _contig(yspec_shape), p.out_dt[j])
+            kb.emit_obuf_flush("obuf", "nv", j, n_ob, p.out_dt[j], f"out{j}",
+                               lambda sx, ys=ys: _elem_off(ys, [(0, "b"), (1, f"t0 + {sx}"), (2, "h"), (3, "m0")]), 1,
+                               (p.M * ELT[p.out_dt[j]]) % 16 == 0 and (t.MB * ELT[p.out_dt[j]]) % 16 == 0)
+        for a, an in enumerate(aux_names):
+            kb.emit_obuf_flush("obuf", "nv", n_out + a, n_ob, DT_F32, "aux",
+                               lambda sx, a=a: _elem_off(aspec, [(0, str(a)), (1, "b"), (2, "h"), (3, f"t0 + {sx}"), (4, "m0")]), 1,
+                               (p.M * 4) % 16 == 0 and (t.MB * 4) % 16 == 0)
     if kb.plain_items:
         w(f"if (c + 1 < {nchunk}) {{")
         w.ind += 1
@@ -1145,7 +1189,11 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     off_wk = off_stage + stage_bytes       # one raw buffer (free again once a chunk is converted)
     off_slots = off_wk + kb.wk_bytes
     off_ring = off_slots + nphys * ns * slot_bytes
-    smem_bytes = off_ring + ring_bytes
+    # per-row gradients written every step (dv ...) are parked next to the ring and stored at flush time
+    row_st = [go for go in grads if go.cls == M1 and not go.over_t and not go.atomic] if redw else []
+    off_ob = off_ring + ring_bytes
+    ob_bytes = ring_bufs * kflush * len(row_st) * p.M * 4
+    smem_bytes = off_ob + ob_bytes
 
     w(_header(prelude))
     mode = f"reverse re-step, resync every {dck} steps" if rev else f"chunk {D} = {nslots} segments x {seg} steps"
@@ -1164,6 +1212,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"float* slots = (float*)(smem + {off_slots});")
     if redw:
         w(f"float* ring = (float*)(smem + {off_ring});")
+        w(f"float* obuf = (float*)(smem + {off_ob}); (void)obuf;")
     has_tma = bool(kb.tma_items)
     w.open("if (tid == 0)")
     w("frnn_mbar_init(&full[0], 1); frnn_mbar_init(&full[1], 1); frnn_mbar_init(&full[2], 1); frnn_mbar_init_fence();")
@@ -1248,6 +1297,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.open("if (rcnt > 0)")
         w("frnn_block_sync();   // all partials of this group are in the ring")
         w(f"const float* rr = ring + rhalf * {kflush * step_floats};")
+        for vi, go in enumerate(row_st):
+            kb.emit_obuf_flush(f"(obuf + rhalf * {kflush * len(row_st) * p.M})", "rcnt", vi, len(row_st), go.spec.dt,
+                               f"dx{go.index}",
+                               lambda sx, go=go: _elem_off(go.spec, [(0, "b"), (1, f"rt_first - {sx}"), (2, "h")]),
+                               go.spec.st(3),
+                               go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)))
         nq = p.N // vw
         stream_vec = [go for go in pm_vec if not go.over_t]
         if stream_vec:
@@ -1402,6 +1457,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             if go.over_t:
                 w("#pragma unroll")
                 w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] += gv{go.index}[r];")
+            elif go in row_st:
+                kb.emit_obuf_put(f"gv{go.index}", "obuf", f"rhalf * {kflush} + rcnt", row_st.index(go), len(row_st))
             else:
                 idx0 = _elem_off(go.spec, [(0, "b"), (1, "t"), (2, "h")])
                 kb.emit_row_vec_store(f"gv{go.index}", go.spec.dt, f"dx{go.index}", idx0, go.spec.st(3),
