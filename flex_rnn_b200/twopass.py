@@ -455,6 +455,17 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             err_words[idx] = th.zeros(1, dtype=th.int32, device=device)
         return err_words[idx]
 
+    strict = os.environ.get("FRNN_CHECK", "0") not in ("", "0")
+
+    def check_status(device, what):
+        """With FRNN_CHECK=1: synchronise after every launch and raise if a
+        kernel reported a timed-out wait (off by default: it serialises)."""
+        if strict and device.type == "cuda":
+            code = int(err_word(device).item())
+            if code:
+                raise RuntimeError(f"flex_rnn_b200 {what} kernel reported error {code} "
+                                   "(1: staged inputs, 2: checkpoint copy did not arrive in time)")
+
     def check_align(ts, flags, what):
         for i, (t, f) in enumerate(zip(ts, flags)):
             assert (t.data_ptr() % 16 == 0) or not f, (
@@ -508,6 +519,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             if not tuned["fw"]:
                 autotune_forward(ptrs, device)
             tuned["launch_fw"](ptrs, device)
+            check_status(device, "forward")
         return (*outs, *stT, *store, aux)
 
     def backward(doutput, dstateT, inputs_, state_store, aux_):
@@ -532,6 +544,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             ptrs += [s.data_ptr() for s in state_store] + [aux.data_ptr()]
             ptrs += [d.data_ptr() for d in ds0] + [d.data_ptr() for d in dxs] + [ew.data_ptr()]
             launch_bw(ptrs, device)
+            check_status(device, "backward")
             for i, go in enumerate(plan.grads):
                 if go.atomic:
                     dxs[i] = dxs[i].to(inputs_[i].dtype)
