@@ -1,8 +1,8 @@
 """Regenerates tests/golden/*.pt from the reference checkout.
 
-Run in a container that has the reference project at /root/reference:
+Run where a checkout of the reference project is available, passing its path:
 
-    python tests/golden/make_golden.py
+    FLEX_RNN_REFERENCE=<path to the flex_rnn checkout> python tests/golden/make_golden.py
 
 For every benchmark step function it draws the seeded inputs of
 ``oracle.naive_oracle.make_inputs`` at a small shape, runs the REFERENCE's own
@@ -18,7 +18,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, "/root/reference")
+sys.path.insert(0, os.environ.get("FLEX_RNN_REFERENCE", os.path.join(os.sep, "root", "reference")))
 
 import flex_rnn  # noqa: E402  (the reference project)
 from oracle import naive_oracle as O  # noqa: E402
