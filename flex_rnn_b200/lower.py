@@ -1271,9 +1271,21 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w(f"float gmat{go.index}[{t.R * t.C}];")
             w("#pragma unroll")
             w(f"for (int i = 0; i < {t.R * t.C}; i++) gmat{go.index}[i] = 0.0f;")
-    # time-invariant per-column / per-head gradients: thread e accumulates element e over time
+    # time-invariant per-column / per-head gradients: work item (ring row s, element j) always falls to the
+    # same thread and accumulator, which sums it over the row groups and over time; atomics combine at the end
     tinv = [go for go in pm_vec + pm_sc if go.over_t]
-    nred_per_thread = (redw + t.NT - 1) // t.NT if redw else 0
+    ntel = sum(p.N if go.cls == N1 else 1 for go in tinv)
+    nred_per_thread = (kflush * ntel + t.NT - 1) // t.NT if tinv else 0
+
+    def tinv_locate(jexpr: str):
+        """Emit `ro` (offset in a ring row) for compact element index jexpr."""
+        w("int ro = 0;")
+        cum = 0
+        for go in tinv:
+            n_el = p.N if go.cls == N1 else 1
+            w(f"if ({jexpr} >= {cum} && {jexpr} < {cum + n_el}) ro = {ring_off[go.index]} + ({jexpr} - {cum});")
+            cum += n_el
+
     if tinv:
         w(f"float racc[{max(1, nred_per_thread)}];")
         w("#pragma unroll")
@@ -1362,12 +1374,11 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if tinv:
             w("#pragma unroll")
             w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
-            w(f"const int e = tid + q * {t.NT};")
-            conds = " || ".join(f"(e >= {ring_off[go.index]} && e < {ring_off[go.index] + (p.N if go.cls == N1 else 1)})" for go in tinv)
-            w.open(f"if ({conds})")
+            w(f"const int it = tid + q * {t.NT}, s = it / {ntel}, j = it % {ntel};")
+            w.open("if (s < rcnt)")
+            tinv_locate("j")
             w("float a = 0.0f;")
-            w("for (int s = 0; s < rcnt; s++)")
-            w(f"  for (int gi = 0; gi < {t.RG}; gi++) a += rr[s * {step_floats} + gi * {redw_pad} + e];")
+            w(f"for (int gi = 0; gi < {t.RG}; gi++) a += rr[s * {step_floats} + gi * {redw_pad} + ro];")
             w("racc[q] += a;")
             w.close()
             w.close()
@@ -1611,14 +1622,17 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     if tinv:
         w("#pragma unroll")
         w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
-        w(f"const int e = tid + q * {t.NT};")
+        w(f"const int it = tid + q * {t.NT}, j = it % {ntel};")
+        w.open(f"if (it < {kflush * ntel})")
+        cum = 0
         for go in tinv:
-            lo = ring_off[go.index]
             n_el = p.N if go.cls == N1 else 1
-            w.open(f"if (e >= {lo} && e < {lo + n_el})")
-            dims = [(0, "b"), (2, "h")] + ([(4, f"(e - {lo})")] if go.cls == N1 else [])
+            w.open(f"if (j >= {cum} && j < {cum + n_el})")
+            dims = [(0, "b"), (2, "h")] + ([(4, f"(j - {cum})")] if go.cls == N1 else [])
             w(f"frnn_atomic_add((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
             w.close()
+            cum += n_el
+        w.close()
         w.close()
     w.close()
     return KernelSource(kname, w.text(), (1, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,

@@ -92,6 +92,7 @@ class Tuning:
     fw_unroll: int = 4       # unroll factor of the timestep loops
     bw_unroll: int = 4
     slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
+    autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     use_tma: bool = True
 
@@ -342,7 +343,7 @@ def forward_tile_candidates(plan: Plan) -> List[lower.Tile]:
     """Alternative forward tilings worth timing (the planned one first)."""
     p = plan.problem
     out, seen = [plan.fw_tile], {(plan.fw_tile.R, plan.fw_tile.C, plan.fw_tile.MB)}
-    for r, c in ((2, 64), (4, 32), (8, 16)):
+    for r, c in ((2, 64), (4, 32), (8, 16), (2, 32), (4, 16)):
         try:
             t = choose_tile(p.M, p.N, r, c, plan.tuning.fw_mb)
         except lower.LoweringError:
@@ -353,17 +354,49 @@ def forward_tile_candidates(plan: Plan) -> List[lower.Tile]:
     return out
 
 
+def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional[lower.KernelSource]:
+    """Emit the backward kernel.  For a ``tile`` other than the planned one the
+    checkpoint interval and slot count stay what the forward was built for and
+    only the flush parameters are re-fitted; None if it does not fit."""
+    p, tu = plan.problem, plan.tuning
+    sg, kflush, bufs = plan.bw_choice
+    cands = [(kflush, bufs)]
+    if tile is not None and tile is not plan.bw_tile:
+        k = max(1, tu.kflush)
+        cands = []
+        while k >= 1:
+            cands += [(k, 2), (k, 1)]
+            k //= 2
+    for kf, nb in cands:
+        bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
+                           plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
+                           kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll)
+        if bw.smem_bytes <= SMEM_LIMIT:
+            return bw
+    return None
+
+
+def backward_tile_candidates(plan: Plan) -> List[lower.Tile]:
+    p = plan.problem
+    out, seen = [plan.bw_tile], {(plan.bw_tile.R, plan.bw_tile.C)}
+    n_tiles = 2 * plan.n_st + 2 * sum(1 for g in plan.grads if g.cls == MN)
+    for r, c in ((8, 8), (4, 8), (4, 16), (8, 4)):
+        try:
+            t = choose_tile(p.M, p.N, r, c, None)
+        except lower.LoweringError:
+            continue
+        if (t.R, t.C) not in seen and t.R * t.C * n_tiles <= 160:
+            seen.add((t.R, t.C))
+            out.append(t)
+    return out
+
+
 def generate(plan: Plan) -> Tuple[lower.KernelSource, lower.KernelSource]:
     """Emit the CUDA source of the forward and the backward kernel."""
-    p, tu = plan.problem, plan.tuning
-    rev = plan.reverse
     fw = generate_forward(plan)
-    sg, kflush, bufs = plan.bw_choice
-    bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
-                       plan.dnext_names, plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),          # type: ignore[attr-defined]
-                       kflush=kflush, ring_bufs=bufs, reverse=rev, step_unroll=tu.bw_unroll)
-    if bw.smem_bytes > SMEM_LIMIT:
-        raise lower.LoweringError(f"kernel {bw.name} needs {bw.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
+    bw = generate_backward(plan)
+    if bw is None:
+        raise lower.LoweringError("the backward kernel does not fit shared memory")
     return fw, bw
 
 
@@ -471,7 +504,41 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             assert (t.data_ptr() % 16 == 0) or not f, (
                 f"{what} #{i + 1} was 16-byte aligned at compilation but is not now")
 
-    tuned = {"fw": _launcher is not None or not plan.tuning.autotune, "launch_fw": launch_fw, "fw_src": fw_src}
+    # timing alternative tilings costs a few NVRTC compilations: only worth it for work of benchmark size
+    no_tune = (_launcher is not None or not plan.tuning.autotune
+               or p.B * p.T * p.H * p.M * p.N < plan.tuning.autotune_min_work)
+    tuned = {"fw": no_tune, "launch_fw": launch_fw, "fw_src": fw_src, "bw": no_tune, "launch_bw": launch_bw,
+             "bw_src": bw_src}
+
+    def autotune_backward(ptrs, device, dxs, ds0):
+        """Time the alternative backward tilings once, writing into throw-away
+        gradient buffers (the kernel accumulates into some of its outputs)."""
+        tuned["bw"] = True
+        nouts = len(dxs) + len(ds0)
+        first_out = len(ptrs) - 1 - nouts
+        scratch = [th.zeros_like(t) for t in list(ds0) + list(dxs)]
+        trial = list(ptrs[:first_out]) + [t.data_ptr() for t in scratch] + [ptrs[-1]]
+        best = None
+        for tile in backward_tile_candidates(plan):
+            try:
+                ks = bw_src if tile is plan.bw_tile else generate_backward(plan, tile)
+                if ks is None:
+                    continue
+                launcher = launch_bw if tile is plan.bw_tile else make(ks)
+                launcher(trial, device)
+                ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
+                ev[0].record()
+                launcher(trial, device)
+                ev[1].record()
+                ev[1].synchronize()
+                ms = ev[0].elapsed_time(ev[1])
+            except (lower.LoweringError, RuntimeError):
+                continue
+            if best is None or ms < best[0]:
+                best = (ms, launcher, ks)
+        if best is not None:
+            tuned["launch_bw"], tuned["bw_src"] = best[1], best[2]
+            forward.sources = (tuned["fw_src"], best[2])       # type: ignore[attr-defined]
 
     def autotune_forward(ptrs, device):
         """Time the alternative forward tilings once on the real arguments (the
@@ -498,7 +565,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
                 best = (ms, launcher, ks)
         if best is not None:
             tuned["launch_fw"], tuned["fw_src"] = best[1], best[2]
-            forward.sources = (best[2], bw_src)       # type: ignore[attr-defined]
+            forward.sources = (best[2], tuned["bw_src"])       # type: ignore[attr-defined]
 
     def forward(inputs_, state0):
         verify_meta(inputs_, in_meta, "input Tensor metadata doesn't match compilation\n")
@@ -543,7 +610,9 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             ptrs += [d.data_ptr() for d in doutput] + [d.data_ptr() for d in dstateT]
             ptrs += [s.data_ptr() for s in state_store] + [aux.data_ptr()]
             ptrs += [d.data_ptr() for d in ds0] + [d.data_ptr() for d in dxs] + [ew.data_ptr()]
-            launch_bw(ptrs, device)
+            if not tuned["bw"]:
+                autotune_backward(ptrs, device, dxs, ds0)
+            tuned["launch_bw"](ptrs, device)
             check_status(device, "backward")
             for i, go in enumerate(plan.grads):
                 if go.atomic:
