@@ -83,13 +83,11 @@ def choose_tile(M: int, N: int, want_r: int, want_c: int, want_mb: Optional[int]
     """Largest legal tile not exceeding the wanted R x C (powers of two)."""
     def pow2_le(x):
         return 1 << (max(1, x).bit_length() - 1)
-    C = min(pow2_le(want_c), N)
-    while N % C:
-        C //= 2
-    while N // C > 32:
-        C *= 2
-    if N % C or 32 % (N // C):
+    # columns per thread: N / L for a power-of-two number of lanes L <= 32, as close to the wish as possible
+    cands = [N // L for L in (1, 2, 4, 8, 16, 32) if N % L == 0]
+    if not cands:
         raise LoweringError(f"N={N} cannot be split over the lanes of a warp")
+    C = min(cands, key=lambda c: (abs(math.log2(c) - math.log2(max(1, want_c))), -c))
     R = min(pow2_le(want_r), M)
     while M % R:
         R //= 2
@@ -110,7 +108,7 @@ def choose_tile(M: int, N: int, want_r: int, want_c: int, want_mb: Optional[int]
             MB = min(M, MB * 2)
             while M % MB:
                 MB += 1
-        elif C > 1 and N // (C // 2) <= 32:
+        elif C > 1 and C % 2 == 0 and N // (C // 2) <= 32:
             C //= 2
         else:
             raise LoweringError(f"state {M}x{N} is too small for a 32-thread CTA")

@@ -99,3 +99,14 @@ def test_unused_and_time_invariant_inputs():
     for a, r in zip(list(dx) + list(ds0), rgx + rgs):
         assert a.shape == r.shape
         assert O.rel_err(a, r) < 1e-5 or float(r.abs().max()) == 0.0 and float(a.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("op,M,N", [("delta_rule", 48, 96), ("rwkv7", 24, 40)])
+def test_sizes_that_are_not_powers_of_two(op, M, N):
+    """96 = 32 lanes x 3 columns, 40 = 8 lanes x 5 columns: any N with a
+    power-of-two divisor <= 32 that leaves whole warps is accepted."""
+    xs, dy, dS = O.make_case(op, 1, 6, 1, M, N, torch.float32)
+    fwd, bwd, _, _ = build_twopass(W.STEPS[op], tuple(xs[:-1]), (xs[-1],), _launcher=EmuLauncher)
+    y, ST, store, aux = fwd(tuple(xs[:-1]), (xs[-1],))
+    dx, ds0 = bwd((dy,), (dS,), tuple(xs[:-1]), (store,), (aux,))
+    check(op, xs, dy, dS, (y, ST, list(dx) + list(ds0)), 1e-5, 1e-5)

@@ -56,6 +56,9 @@ CASES = [
     ("mamba2", 2, 19, 2, 32, 64, torch.float32),
     ("delta_rule", 1, 24, 2, 64, 64, torch.float16),
     ("delta_rule", 1, 1, 1, 32, 32, torch.float32),         # a single timestep
+    ("delta_rule", 2, 21, 2, 48, 96, torch.float32),        # sizes that are not powers of two
+    ("rwkv7", 1, 10, 2, 24, 40, torch.bfloat16),
+    ("gated_delta_rule", 1, 70, 1, 256, 64, torch.float32),  # tall state, several checkpoint chunks
 ]
 
 
