@@ -249,28 +249,58 @@ def main():
     pdy, pdS = dy_host.pin_memory(), dS_host.pin_memory()
     out_host = None
 
-    def e2e_step():
+    # Three streams, two buffer sets: the host->device copy of step i+1 and the device->host copy of step
+    # i-1 run beside the kernels of step i (all of them inside the timed region).
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    host_in = pin + [pdy, pdS]
+    dev_in = [[torch.empty_like(p, device=dev) for p in host_in] for _ in range(2)]
+    dev_out = [None, None]
+    ev_in = [torch.cuda.Event() for _ in range(2)]       # inputs of the slot are on the device
+    ev_used = [torch.cuda.Event() for _ in range(2)]     # the kernels are done with the slot's inputs
+    ev_done = [torch.cuda.Event() for _ in range(2)]     # results of the slot are staged
+    ev_out = [torch.cuda.Event() for _ in range(2)]      # results of the slot have reached the host
+
+    def e2e_step(i):
         nonlocal out_host
-        d = [p.to(dev, non_blocking=True).requires_grad_() for p in pin]
-        gy, gS = pdy.to(dev, non_blocking=True), pdS.to(dev, non_blocking=True)
+        k = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_used[k])
+            for d_, h_ in zip(dev_in[k], host_in):
+                d_.copy_(h_, non_blocking=True)
+            ev_in[k].record(s_in)
+        stream.wait_event(ev_in[k])
+        stream.wait_event(ev_out[k])
+        d = [t.detach().requires_grad_() for t in dev_in[k][:-2]]
         y, ST = op(*d)
-        grads = torch.autograd.grad([y, ST], d, [gy, gS])
+        grads = torch.autograd.grad([y, ST], d, [dev_in[k][-2], dev_in[k][-1]])
         res = [y, ST, *grads]
+        if dev_out[k] is None:
+            dev_out[k] = [torch.empty_like(r) for r in res]
         if out_host is None:
             out_host = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
-        for h, r in zip(out_host, res):
-            h.copy_(r.detach(), non_blocking=True)
-        return res
+        for o_, r in zip(dev_out[k], res):
+            o_.copy_(r.detach())
+        ev_used[k].record(stream)
+        ev_done[k].record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done[k])
+            for h, o_ in zip(out_host, dev_out[k]):
+                h.copy_(o_, non_blocking=True)
+            ev_out[k].record(s_out)
 
-    n_e2e = 0 if args.no_e2e else max(3, min(args.steps, 10))
-    for _ in range(0 if args.no_e2e else 2):
-        e2e_step()
+    n_e2e = 0 if args.no_e2e else max(4, min(args.steps, 20))
+    for i in range(0 if args.no_e2e else 4):
+        e2e_step(i)
+    torch.cuda.synchronize(dev)
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(n_e2e):
-        e2e_step()
+    for i in range(n_e2e):
+        e2e_step(i)
+    stream.wait_stream(s_out)          # the last results must have reached the host
+    stream.wait_stream(s_in)
     e1.record(stream)
+    torch.cuda.synchronize(dev)
     sync_all()
     e2e_ms = torch.tensor([e0.elapsed_time(e1) / max(1, n_e2e)], device=dev)
     if world > 1:

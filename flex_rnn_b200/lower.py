@@ -287,18 +287,20 @@ class Body:
         self.shape[name] = s
         self.w(f"float {vname(name)}[{self.size(s)}];")
 
+    col_major = False      # full-tile loops: columns outermost (consecutive FMAs share the row-vector operand)
+
     def loops(self, s: Shape, body):
         w = self.w
-        if s[0]:
-            w("#pragma unroll")
-            w.open(f"for (int r = 0; r < {self.t.R}; r++)")
-        if s[1]:
-            w("#pragma unroll")
-            w.open(f"for (int c = 0; c < {self.t.C}; c++)")
+        order = [(1, "c", self.t.C), (0, "r", self.t.R)] if (Body.col_major and s == MN) else \
+                [(0, "r", self.t.R), (1, "c", self.t.C)]
+        opened = 0
+        for dim, var, ext in order:
+            if s[dim]:
+                w("#pragma unroll")
+                w.open(f"for (int {var} = 0; {var} < {ext}; {var}++)")
+                opened += 1
         w(body("r" if s[0] else "0", "c" if s[1] else "0"))
-        if s[1]:
-            w.close()
-        if s[0]:
+        for _ in range(opened):
             w.close()
 
     def _check_partial(self, n: Node) -> bool:

@@ -92,6 +92,7 @@ class Tuning:
     fw_unroll: int = 4       # unroll factor of the timestep loops
     bw_unroll: int = 4
     slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
+    col_major: int = 0       # emit full-tile loops with columns outermost
     autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     use_tma: bool = True
@@ -323,6 +324,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
 def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None) -> lower.KernelSource:
     """Emit the forward kernel (for ``tile`` instead of the planned tile if given)."""
     p, tu = plan.problem, plan.tuning
+    lower.Body.col_major = bool(tu.col_major)
     tile = tile or plan.fw_tile
     # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
     stage = tu.fw_stage
@@ -359,6 +361,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
     checkpoint interval and slot count stay what the forward was built for and
     only the flush parameters are re-fitted; None if it does not fit."""
     p, tu = plan.problem, plan.tuning
+    lower.Body.col_major = bool(tu.col_major)
     sg, kflush, bufs = plan.bw_choice
     cands = [(kflush, bufs)]
     if tile is not None and tile is not plan.bw_tile:
