@@ -22,6 +22,12 @@ sample (`cpu_baseline`).
 `--impl reference` times the CPU oracle (the restatement of the reference's
 `jit.naive` + autograd, which is the reference's only CPU implementation of
 this path) on a bounded sample of the same workload, on all host threads.
+
+`--impl reference_cuda` times the unmodified reference package's own generated
+CUDA kernels (through its `jit` object) on the same GPU, workload and inputs,
+when an install of it is present under `baseline/_ref` (not part of this
+repository); otherwise it prints an `unavailable` line.  It is the GPU kernel
+this backend replaces, reported beside the CPU baseline.
 """
 import argparse
 import json
@@ -136,12 +142,71 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_cuda(args, rank, world, local):
+    """fwd+bwd of the reference package's own compiled path, timed like the main arm (device events, max over ranks)."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    opname, B, T, H, M, N = WORKLOADS[args.op]
+    try:
+        if not os.path.isdir(os.path.join(ref_dir, "flex_rnn")):
+            raise RuntimeError("no reference install under baseline/_ref")
+        sys.path.insert(0, ref_dir)
+        import torch
+        import torch.distributed as dist
+        import flex_rnn
+        from flex_rnn_b200 import workloads as W
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=dev)
+        xs, dy, dS = W.synthetic(opname, B, T, H, M, N, torch.bfloat16, seed=rank)
+        leaves = [x.to(dev).requires_grad_() for x in xs]
+        dy, dS = dy.to(dev), dS.to(dev)
+        op = flex_rnn.jit(W.STEPS[opname])
+
+        def step():
+            y, ST = op(*leaves)
+            return torch.autograd.grad([y, ST], leaves, [dy.to(y.dtype), dS])
+        # the reference builds its extension in a fixed directory: let rank 0 build, then the others load it
+        for turn in range(2 if world > 1 else 1):
+            if world == 1 or (rank == 0) == (turn == 0):
+                step()
+            if world > 1:
+                dist.barrier()
+        for _ in range(max(args.warmup, 3)):
+            step()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        times = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            times.append(e0.elapsed_time(e1))
+        ms = torch.tensor([sum(times) / len(times)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.destroy_process_group()
+        ms = float(ms)
+        if rank == 0:
+            print(json.dumps({"impl": "reference_cuda", "metric": METRIC, "value": world * B * T / (ms / 1e3), "unit": UNIT,
+                              "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+                              "config": {"workload": f"{args.op} B{B} T{T} H{H} {M}x{N} bf16 I/O, fp32 math, per GPU",
+                                         "l2": "256 MiB flush write between timed steps"}}), flush=True)
+    except Exception as e:  # the reference is not part of this repository: report, do not fail
+        if rank == 0:
+            print(json.dumps({"impl": "reference_cuda", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"])
     ap.add_argument("--op", default="delta_rule", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the benchmark's 8); smaller = profiling case")
@@ -157,6 +222,9 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.impl == "reference_cuda":
+        run_reference_cuda(args, rank, world, local)
         return
 
     import torch

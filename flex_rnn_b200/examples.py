@@ -16,7 +16,7 @@ from flex_rnn_b200 import workloads as W
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ops = list(W.STEPS) + [k for k in W.ZOO if k != "mlstm_gates"]
+    ops = list(W.STEPS) + list(W.ZOO)
     ap.add_argument("--op", default="rwkv7", choices=ops)
     ap.add_argument("--batchsz", type=int, default=8)
     ap.add_argument("--modeldim", type=int, default=None)
@@ -40,7 +40,7 @@ def main(argv=None):
         xs, _, _ = W.synthetic(a.op, B, T, H, 64 if a.op == "mamba2" else C, C, dtype)
         step_fn, nst = W.STEPS[a.op], 1
     else:
-        M, N = (modeldim, 1) if a.op in ("rwkv4", "hgrn") else (C, 16 if a.op == "mamba" else C)
+        M, N = (modeldim, 1) if a.op in ("rwkv4", "hgrn") else (1, 1) if a.op == "mlstm_gates" else (C, 16 if a.op == "mamba" else C)
         Hh = 1 if a.op in ("rwkv4", "hgrn") else H
         ins, sts = W.zoo_case(a.op, B, T, Hh, M, N, dtype)
         xs, step_fn, nst = ins + sts, W.ZOO[a.op], len(sts)

@@ -453,6 +453,89 @@ class _device_ctx:
             self.ctx.__exit__(*a)
 
 
+def _padded_rows(inputs, state) -> Optional[int]:
+    """Row count a state too small for one warp is padded to, else None.
+
+    A CTA is at least one warp; a row is spread over at most 32 lanes (a power
+    of two dividing N), so M x lanes must be a multiple of 32."""
+    M = max(i.shape[-2] for i in tuple(inputs) + tuple(state))
+    N = max(i.shape[-1] for i in tuple(inputs) + tuple(state))
+    lanes = max(L for L in (1, 2, 4, 8, 16, 32) if N % L == 0)
+    k = 1
+    while (M * k * lanes) % 32:
+        k += 1
+    return None if k == 1 else M * k
+
+
+def _build_row_padded(step, inputs, state, Mp, dryrun, tuning, _launcher):
+    """build_twopass for a state with fewer elements than one warp has threads
+    (the 1x1 gate recurrence of an mLSTM, say).
+
+    The recurrence is run on ``Mp`` rows: the real rows, repeated.  Repeated rows
+    compute the same finite values as the rows they copy; their upstream
+    gradients are zero, so they add nothing to the gradients summed over rows,
+    and their outputs and state rows are dropped.  The copies this costs are of
+    the small tensors that carry a row dimension."""
+    inputs, state = tuple(inputs), tuple(state)
+    M = max(i.shape[-2] for i in inputs + state)
+
+    def rep(x, dim):
+        if x.shape[dim] == 1 and M > 1:
+            return x                      # broadcast over rows already
+        if x.device.type == "meta" or dryrun:
+            shape = list(x.shape)
+            shape[dim] = Mp
+            return th.empty(shape, dtype=x.dtype, device=x.device)
+        return x.index_select(dim, th.arange(Mp, device=x.device) % x.shape[dim])
+
+    # an input without a row dimension stays as it is (M == 1: every input is one, the state alone is padded)
+    def pad_inputs(xs):
+        return tuple(x if x.shape[-2] == 1 else rep(x, -2) for x in xs)
+
+    def pad_state(ss):
+        return tuple(rep(s_, -2) for s_ in ss)
+
+    inner = build_twopass(step, pad_inputs(inputs), pad_state(state), dryrun, tuning, _launcher)
+    fw_meta_p, bw_meta_p = inner[-2:]
+    nst, nin = len(state), len(inputs)
+    nout = len(fw_meta_p) - 2 * nst - 1
+    B, T, H = fw_meta_p[0][0][:3] if nout else (state[0].shape[0], max(i.shape[1] for i in inputs), state[0].shape[1])
+    out_meta = tuple(th.empty(B, T, H, M, dtype=m[2], device="meta") for m in fw_meta_p[:nout])
+    stT_meta = tuple(th.empty_like(s_, device="meta") for s_ in state)
+    fw_meta = get_meta([*out_meta, *stT_meta]) + tuple(fw_meta_p[nout + nst:])
+    dx_meta = tuple(th.empty_like(x, device="meta") for x in inputs)
+    bw_meta = get_meta([*dx_meta, *stT_meta])
+    if dryrun:
+        return fw_meta, bw_meta
+    fwd_p, bwd_p = inner[:2]
+    in_meta = tuple(th.empty_strided(x.shape, x.stride(), dtype=x.dtype, device="meta") for x in inputs)
+    st_meta = tuple(th.empty_strided(x.shape, x.stride(), dtype=x.dtype, device="meta") for x in state)
+
+    def forward(inputs_, state0):
+        verify_meta(inputs_, in_meta, "input Tensor metadata doesn't match compilation\n")
+        verify_meta(state0, st_meta, "initial state Tensor metadata doesn't match compilation\n")
+        res = fwd_p(pad_inputs(inputs_), pad_state(state0))
+        outs = tuple(o[..., :M].contiguous() for o in res[:nout])
+        stT = tuple(th.empty_like(s0).copy_(sp[:, :, :M]) for s0, sp in zip(state0, res[nout:nout + nst]))
+        return (*outs, *stT, *res[nout + nst:])
+
+    def backward(doutput, dstateT, inputs_, state_store, aux_):
+        verify_meta(inputs_, in_meta)
+        dout_p = tuple(th.nn.functional.pad(d, (0, Mp - M)) for d in doutput)
+        dst_p = tuple(th.nn.functional.pad(d, (0, 0, 0, Mp - M)) for d in dstateT)
+        dxs_p, ds0_p = bwd_p(dout_p, dst_p, pad_inputs(inputs_), state_store, aux_)
+        dxs = tuple(dp if dp.shape == x.shape else th.empty_like(x).copy_(dp.narrow(-2, 0, x.shape[-2]))
+                    for dp, x in zip(dxs_p, inputs_))
+        ds0 = tuple(th.empty_strided(m.shape, m.stride(), dtype=m.dtype, device=dp.device).copy_(dp[:, :, :M])
+                    for m, dp in zip(stT_meta, ds0_p))
+        return dxs, ds0
+
+    for name in ("plan", "sources", "launchers", "kernel_status"):
+        setattr(forward, name, getattr(fwd_p, name))
+    forward.padded_rows = Mp                # type: ignore[attr-defined]
+    return forward, backward, fw_meta, bw_meta
+
+
 def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = None, _launcher=None):
     """See the module docstring.  With ``dryrun`` nothing touches CUDA.
 
@@ -462,6 +545,9 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
     check it without a GPU).  Library code never passes it, and without it
     tensors that are not on a CUDA device are rejected.
     """
+    Mp = _padded_rows(inputs, state)
+    if Mp is not None:
+        return _build_row_padded(step, inputs, state, Mp, dryrun, tuning, _launcher)
     plan, fw_meta, bw_meta = make_plan(step, inputs, state, tuning)
     if dryrun:
         return fw_meta, bw_meta

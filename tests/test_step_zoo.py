@@ -42,11 +42,40 @@ def test_emulated(op):
         assert O.rel_err(a, b) < 1e-5
 
 
+@pytest.mark.parametrize("op,M,N", [("mlstm_gates", 1, 1), ("hgrn", 4, 1), ("gla", 2, 4)])
+def test_emulated_small_state(op, M, N):
+    """States with fewer elements than a warp has threads (the reference runs
+    them with one thread per element, twopass.py:154-164) go through the same
+    kernels on repeated rows; three outputs for the mLSTM gates."""
+    from emu.emu import EmuLauncher
+    from flex_rnn_b200.twopass import verify_meta
+    ins, sts = W.zoo_case(op, 2, 7, 2, M, N)
+    tu = Tuning(fw_r=2, fw_c=4, fw_mb=16, fw_stage=4, bw_r=2, bw_c=4, seg=2, nslots=2)
+    fwd, bwd, fm, bm = build_twopass(W.ZOO[op], tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
+    assert fwd.padded_rows % M == 0 and fwd.padded_rows > M
+    meta = tuple(x.to("meta") for x in ins), tuple(s.to("meta") for s in sts)
+    assert build_twopass(W.ZOO[op], *meta, dryrun=True) == (fm, bm)
+    res = fwd(tuple(ins), tuple(sts))
+    ns = len(sts)
+    no = len(res) - 2 * ns - 1
+    assert no == (3 if op == "mlstm_gates" else 1)
+    g = torch.Generator().manual_seed(1)
+    dys = [torch.randn(y.shape, generator=g) for y in res[:no]]
+    dSs = [torch.randn(s.shape, generator=g) for s in sts]
+    dx, ds0 = bwd(tuple(dys), tuple(dSs), tuple(ins), tuple(res[no + ns:no + 2 * ns]), (res[-1],))
+    verify_meta(res, [torch.empty_strided(a, b, dtype=c) for a, b, c in fm])
+    verify_meta(list(dx) + list(ds0), [torch.empty_strided(a, b, dtype=c) for a, b, c in bm])
+    ry, rST, rgx, rgs = oracle(op, ins, sts, dys, dSs)
+    for a, b in zip(list(res[:no + ns]) + list(dx) + list(ds0), list(ry) + list(rST) + rgx + rgs):
+        assert a.shape == b.shape
+        assert O.rel_err(a, b) < 1e-5
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("op", [k for k in W.ZOO if k != "mlstm_gates"])
+@pytest.mark.parametrize("op", list(W.ZOO))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gpu(op, dtype):
-    M, N = (256, 1) if op in ("rwkv4", "hgrn") else (64, 64)
+    M, N = (256, 1) if op in ("rwkv4", "hgrn") else (1, 1) if op == "mlstm_gates" else (64, 64)
     ins, sts = W.zoo_case(op, 2, 40, 3, M, N, dtype)
     dev = "cuda:0"
     leaves = [x.to(dev).requires_grad_() for x in ins + sts]
@@ -70,3 +99,83 @@ def test_gpu(op, dtype):
             assert float(a.float().abs().max()) == 0.0
         else:
             assert O.rel_err(a, b) < tol_grad, (op, O.rel_err(a, b))
+
+
+def _mlstm(step1, step2, step3, q, k, v, i, f, sa, sb, sc):
+    """The three-kernel mLSTM pipeline of the reference's examples
+    (tests/examples.py:396-426): gates on a 1x1 state, the normaliser on a
+    one-row state, then the matrix state; layout adaptors are views."""
+    C = q.shape[-1]
+    i, f, sb, sc = [x.unsqueeze(-1) for x in [i, f, sb, sc]]
+    q, k, v, i, f = [x.transpose(1, 2).unsqueeze(-2) for x in [q, k, v, i, f]]
+    i, f, sc, scT = step1(i, f, sc)
+    i, f = i.unsqueeze(-1), f.unsqueeze(-1)
+    sb_q, sbT = step2(k, q, i, f, sb.mT)
+    norm = 1 / (torch.maximum(torch.abs(sb_q), (-sc).exp() * C ** .5) + 1e-6 * C ** .5).unsqueeze(-1)
+    y, saT = step3(q, k, v.mT, i, f, norm, sa.mT)
+    return y.transpose(1, 2), saT.mT, sbT.squeeze(-2), scT.squeeze(-1)
+
+
+def _mlstm_steps():
+    def step2(k, q, i, f, sb):
+        sb_ = f * sb + i * k
+        return (sb_ * q).sum(-1, True), sb_
+
+    def step3(q, k, v, i, f, norm, sa):
+        sa_ = f * sa + i * v * k
+        return (norm * q * sa_).sum(-1, True), sa_
+    return W.mlstm_gates, step2, step3
+
+
+def _gsa(step1, step2, q, k, v, x, g, sa, sb):
+    """Two chained kernels with a softmax between them (tests/examples.py:356-371)."""
+    q, k, v, x, g = [i.unsqueeze(-2) for i in [q, k, v, x, g]]
+    qv, sa = step1(q, k, x.mT, g.mT, sa.mT)
+    qv = qv.softmax(-1).unsqueeze(-2)
+    y, sb = step2(qv.to(q.dtype), x, v.mT, g, sb.mT)
+    return y, sa.mT, sb.mT
+
+
+def _gsa_steps():
+    def step1(q, k, x, g, s):
+        s = g.exp() * s + x * k
+        return (s * q).sum(-1, True), s
+
+    def step2(q, x, v, g, s):
+        s = g.exp() * s + v * x
+        return (s * q).sum(-1, True), s
+    return step1, step2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["mlstm", "gsa"])
+def test_gpu_pipelines(name):
+    """Multi-kernel callers: every stage compiled by this backend, chained
+    through views and ordinary torch ops, differentiated end to end, against
+    the same pipeline on the naive scans in fp64."""
+    B, T, H, C = 2, 24, 3, 32
+    g = torch.Generator().manual_seed(3)
+    n = lambda *s: torch.randn(*s, generator=g)
+    if name == "mlstm":
+        args = [n(B, H, T, C), n(B, H, T, C) / C ** .5, n(B, H, T, C), n(B, H, T), n(B, H, T) + 2,
+                n(B, H, C, C), n(B, H, C), n(B, H, 1)]
+        steps, pipe = _mlstm_steps(), _mlstm
+    else:
+        args = [n(B, T, H, C), n(B, T, H, C), n(B, T, H, C), n(B, T, H, C), -torch.sigmoid(n(B, T, H, C)),
+                n(B, H, C, C), n(B, H, C, C)]
+        steps, pipe = _gsa_steps(), _gsa
+    dev = "cuda:0"
+    ops = [flex_rnn_b200.jit(s) for s in steps]
+    leaves = [a.to(dev).requires_grad_() for a in args]
+    outs = pipe(*ops, *leaves)
+    ups = [torch.randn(o.shape, generator=g) for o in outs]
+    grads = torch.autograd.grad(list(outs), leaves, [u.to(dev) for u in ups])
+    torch.cuda.synchronize()
+    for o in ops:
+        assert o.forward_func.kernel_status(dev) == 0
+    ref_leaves = [a.double().requires_grad_() for a in args]
+    ref_outs = pipe(*[o.naive_fp64 for o in ops], *ref_leaves)
+    ref_grads = torch.autograd.grad(list(ref_outs), ref_leaves, [u.double() for u in ups])
+    for a, b in zip(list(outs) + list(grads), list(ref_outs) + list(ref_grads)):
+        assert a.shape == b.shape
+        assert O.rel_err(a, b) < 5e-5, (name, O.rel_err(a, b))
