@@ -699,11 +699,16 @@ class KernelBuilder:
             vw = 4 if ln % 4 == 0 else (2 if ln % 2 == 0 else 1)   # elements per thread and iteration
             w.open(f"for (int e = tid; e < {nv} * {ln // vw}; e += {t.NT})")
             w(f"const int tl = e / {ln // vw}, i = (e % {ln // vw}) * {vw}; (void)i;")
+
+            def one(c, cls=cls):
+                # a value of another class inside this loop has one element (a column vector of a one-row state,
+                # say): it is read like a scalar
+                return c == S11 or c != cls
             for nm in order:
                 hn = "h_" + nm.replace(".", "_")
                 if nm in hoisted:
                     n = hoisted[nm]
-                    width = vw if n.shape != S11 else 1
+                    width = 1 if one(n.shape) else vw
                     w(f"float {hn}[{width}];")
                     for q in range(width):
                         ops = []
@@ -711,14 +716,14 @@ class KernelBuilder:
                             if not isinstance(a, str):
                                 ops.append(flit(a))
                             else:
-                                aw = vw if self.avail[a] != S11 else 1
+                                aw = 1 if one(self.avail[a]) else vw
                                 ops.append(f"h_{a.replace('.', '_')}[{q if aw > 1 else 0}]")
                         w(f"{hn}[{q}] = {op_expr(n, ops)};")
                 elif nm in self.const_scalars:
                     w(f"float {hn}[1]; {hn}[0] = {self.const_scalars[nm]};")
                 else:
                     it = self.item_by_key[nm]
-                    if it.cls == S11:
+                    if one(it.cls):
                         w(f"float {hn}[1]; {hn}[0] = frnn_io<{it.dt}>::ld({raw} + {it.off} + tl * {it.rowb}, 0);")
                     else:
                         w(f"float {hn}[{vw}]; frnn_ldv<{it.dt},{vw}>({raw} + {it.off} + tl * {it.rowb}, i, {hn});")

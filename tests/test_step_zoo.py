@@ -71,6 +71,28 @@ def test_emulated_small_state(op, M, N):
         assert O.rel_err(a, b) < 1e-5
 
 
+@pytest.mark.parametrize("M,N", [(1, 32), (1, 64), (32, 1)])
+def test_emulated_one_row_or_column_state(M, N):
+    """A state of one row ([B,H,1,N]: the mLSTM normaliser) makes the output
+    gradient a single value per step and every column input a scalar; a state of
+    one column does the same to the row inputs."""
+    from emu.emu import EmuLauncher
+    step2 = _mlstm_steps()[1]
+    B, T, H = 2, 12, 2
+    g = torch.Generator().manual_seed(5)
+    n = lambda *s: torch.randn(*s, generator=g)
+    ins = (n(B, T, H, 1, N), n(B, T, H, 1, N), n(B, T, H, 1, 1), torch.sigmoid(n(B, T, H, 1, 1)))
+    for step, xs in ((step2, ins), (W.delta_rule, (ins[0] / N ** .5, ins[1] / N ** .5, n(B, T, H, M, 1), ins[3]))):
+        sts = (n(B, H, M, N),)
+        fwd, bwd, _, _ = build_twopass(step, xs, sts, _launcher=EmuLauncher)
+        res = fwd(xs, sts)
+        dys, dSs = [n(*res[0].shape)], [n(*sts[0].shape)]
+        dx, ds0 = bwd(tuple(dys), tuple(dSs), xs, (res[2],), (res[3],))
+        ry, rST, rgx, rgs = O.fwd_bwd(step, list(xs), list(sts), dys, dSs, dtype=torch.float64)
+        for a, b in zip(list(res[:2]) + list(dx) + list(ds0), list(ry) + list(rST) + rgx + rgs):
+            assert a.shape == b.shape and O.rel_err(a, b) < 1e-5
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("op", list(W.ZOO))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
