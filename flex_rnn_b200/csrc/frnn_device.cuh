@@ -96,6 +96,12 @@ FRNN_DEV void frnn_report(int* err, int code) { atomicCAS(err, 0, code); }
 FRNN_DEV float frnn_expf(float x) { return __expf(x); }
 FRNN_DEV float frnn_logf(float x) { return __logf(x); }
 FRNN_DEV float frnn_sqrtf(float x) { return __fsqrt_rn(x); }
+// packed fp32x2 arithmetic (sm_100: one instruction, two lanes)
+typedef float2 frnn_pk;
+FRNN_DEV frnn_pk frnn_pk_make(float a, float b) { return make_float2(a, b); }
+FRNN_DEV frnn_pk frnn_fma2(frnn_pk a, frnn_pk b, frnn_pk c) { return __ffma2_rn(a, b, c); }
+FRNN_DEV frnn_pk frnn_mul2(frnn_pk a, frnn_pk b) { return __fmul2_rn(a, b); }
+FRNN_DEV frnn_pk frnn_add2(frnn_pk a, frnn_pk b) { return __fadd2_rn(a, b); }
 FRNN_DEV float frnn_rcpf(float x) { return __frcp_rn(x); }
 FRNN_DEV float frnn_divf(float a, float b) { return __fdividef(a, b); }
 #endif  // !FRNN_EMU

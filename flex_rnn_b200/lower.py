@@ -25,7 +25,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 from .graph import MN, M1, N1, S11, Node, Shape, StepGraph
 
@@ -265,6 +265,116 @@ class Body:
         self.shape = dict(shapes)
         self.partial: Dict[str, bool] = {}     # value is a per-row-group partial sum
         self.alias: Dict[str, str] = {}        # value name -> name of the register tile that holds it
+        self.fused: Dict[str, Node] = {}       # products folded into the packed FMA of their only consumer
+
+    # -- packed fp32x2 arithmetic (sm_100 `fma.rn.f32x2`) ---------------------------------------
+    # Values that vary along the columns are processed two columns at a time: one packed instruction
+    # does the work of two scalar ones, which halves the issue slots the arithmetic needs (the scan
+    # kernels are issue-bound, not pipe-bound).  The register arrays stay scalar; a pair is
+    # (x[c], x[c+1]) and ptxas allocates it to an aligned register pair.
+    pack2 = False
+
+    def can_pack(self) -> bool:
+        return Body.pack2 and self.t.C % 2 == 0
+
+    def varies_c(self, a) -> bool:
+        return isinstance(a, str) and bool(self.shape[a][1])
+
+    def pair(self, a, r: str, c: str, neg: bool = False) -> str:
+        """float2 expression of operand ``a`` at columns (c, c+1) of row r."""
+        sg = "-" if neg else ""
+        if self.varies_c(a):
+            assert not neg
+            return f"frnn_pk_make({self.at(a, r, c)}, {self.at(a, r, c + ' + 1')})"
+        x = self.at(a, r, c)
+        return f"frnn_pk_make({sg}({x}), {sg}({x}))"
+
+    def fuse_group(self, group: Sequence[Node], all_nodes: Sequence[Node], keep: Iterable[str]):
+        """Choose the products of ``group`` to fold into their consumer: a
+        product used exactly once, by an add / sub of its own shape or by a sum,
+        emitted in the same group, and not needed by anyone else."""
+        if not self.can_pack():
+            return
+        keep = set(keep)
+        uses: Dict[str, int] = {}
+        for n in all_nodes:
+            for a in n.value_args():
+                uses[a] = uses.get(a, 0) + 1
+        by_name = {n.name: n for n in group}
+        for u in group:
+            for a in u.value_args():
+                m = by_name.get(a)
+                if m is None or m.op != "mul" or uses.get(a, 0) != 1 or a in keep or not m.shape[1]:
+                    continue
+                ok = False
+                if u.op == "add" and u.shape == m.shape:
+                    ok = True
+                elif u.op == "sub" and u.shape == m.shape:
+                    other = u.args[0] if u.args[1] == a else u.args[1]
+                    if u.args[1] == a:            # z - x*y: negate a factor that is cheap to negate
+                        ok = any(not self.varies_c_node(x, by_name, all_nodes) for x in m.args)
+                    else:                         # x*y - z
+                        ok = not self.varies_c_node(other, by_name, all_nodes)
+                elif u.op == "sum" and u.args[0] == a:
+                    ok = self._pair_sum_mode(u, m.shape) is not None
+                if ok:
+                    self.fused[a] = m
+                    break                         # one product per consumer
+
+    def varies_c_node(self, a, by_name, all_nodes) -> bool:
+        if not isinstance(a, str):
+            return False
+        if a in self.shape:
+            return bool(self.shape[a][1])
+        for n in all_nodes:
+            if n.name == a:
+                return bool(n.shape[1])
+        return True
+
+    def _fma_operands(self, u: Node, r: str, c: str) -> Optional[Tuple[str, str, str]]:
+        """(X, Y, Z) with u = X*Y + Z for an add / sub with a folded product."""
+        for k, a in enumerate(u.args):
+            if isinstance(a, str) and a in self.fused:
+                m, z = self.fused[a], u.args[1 - k]
+                x, y = m.args
+                if u.op == "add":
+                    return self.pair(x, r, c), self.pair(y, r, c), self.pair(z, r, c)
+                if k == 1:                        # z - x*y
+                    if not self.varies_c(x):
+                        return self.pair(x, r, c, neg=True), self.pair(y, r, c), self.pair(z, r, c)
+                    return self.pair(x, r, c), self.pair(y, r, c, neg=True), self.pair(z, r, c)
+                return self.pair(x, r, c), self.pair(y, r, c), self.pair(z, r, c, neg=True)   # x*y - z
+        return None
+
+    def pair_expr(self, n: Node, r: str, c: str) -> Optional[str]:
+        """Packed expression of an elementwise node, or None if it has none."""
+        if n.op not in ("add", "sub", "mul") or not n.shape[1]:
+            return None
+        f = self._fma_operands(n, r, c) if n.op in ("add", "sub") else None
+        if f:
+            return f"frnn_fma2({f[0]}, {f[1]}, {f[2]})"
+        a, b = n.args
+        if n.op == "mul":
+            return f"frnn_mul2({self.pair(a, r, c)}, {self.pair(b, r, c)})"
+        if n.op == "add":
+            return f"frnn_add2({self.pair(a, r, c)}, {self.pair(b, r, c)})"
+        if not self.varies_c(b):
+            return f"frnn_add2({self.pair(a, r, c)}, {self.pair(b, r, c, neg=True)})"
+        return f"frnn_fma2({self.pair(b, r, c)}, frnn_pk_make(-1.0f, -1.0f), {self.pair(a, r, c)})"
+
+    def pair_loops(self, s: Shape, body):
+        """Like loops() for a column-varying shape, two columns per iteration."""
+        w = self.w
+        opened = 0
+        if s[0]:
+            w("#pragma unroll")
+            w.open(f"for (int r = 0; r < {self.t.R}; r++)")
+            opened += 1
+        w("#pragma unroll")
+        w.open(f"for (int c = 0; c < {self.t.C}; c += 2)")
+        w(body("r" if s[0] else "0", "c"))
+        for _ in range(opened + 1):
+            w.close()
 
     # element accessor of a value (or literal) at tile position (r, c)
     def at(self, a, r: str, c: str) -> str:
@@ -332,6 +442,13 @@ class Body:
 
     def node(self, n: Node, allow_over_m: bool):
         w, t = self.w, self.t
+        if n.name in self.fused:
+            # evaluated inside its consumer; only the bookkeeping happens here
+            self.partial[n.name] = self._check_partial(n)
+            self.shape[n.name] = n.shape
+            return
+        if n.op == "sum" and self.can_pack() and self._pair_sum(n, allow_over_m):
+            return
         if n.op == "sum":
             src = n.args[0]
             ss = self.shape[src]
@@ -403,9 +520,102 @@ class Body:
             return
         self.partial[n.name] = self._check_partial(n)
         self.declare(n.name, n.shape)
+        if self.can_pack() and self.pair_expr(n, "r", "c") is not None:
+            self.pair_loops(n.shape, lambda r, c: (
+                f"{{ const frnn_pk v2 = {self.pair_expr(n, r, c)}; "
+                f"{self.at(n.name, r, c)} = v2.x; {self.at(n.name, r, c + ' + 1')} = v2.y; }}"))
+            return
         self.loops(n.shape, lambda r, c: f"{self.at(n.name, r, c)} = {op_expr(n, [self.at(x, r, c) for x in n.args])};")
 
-    def graph(self, g: StepGraph, allow_over_m: bool = False):
+    @staticmethod
+    def _pair_sum_mode(n: Node, ss: Shape) -> Optional[Tuple[bool, bool]]:
+        """(rows reduced, columns reduced) if the packed form applies to this sum."""
+        if not ss[1]:
+            return None
+        red_r = bool(n.over_m and ss[0])
+        red_c = bool(n.over_n)
+        if not (red_r or red_c) or (n.shape[1] and red_c):
+            return None
+        return red_r, red_c
+
+    def _pair_sum(self, n: Node, allow_over_m: bool) -> bool:
+        """Sum of a column-varying value with packed accumulators: over the
+        columns (both lanes are partial sums, added at the end) or over the rows
+        (the kept columns go in pairs).  False: not applicable, use the scalar form."""
+        w, t = self.w, self.t
+        src = n.args[0]
+        ss = self.shape[src]
+        mode = self._pair_sum_mode(n, ss)
+        if mode is None:
+            return False
+        red_r, red_c = mode
+        if n.over_m and not allow_over_m:
+            raise LoweringError("Only torch.sum(x, dim=-1, keepdim=True) is supported in the forward pass")
+        if n.over_m and self.partial.get(src, False):
+            raise LoweringError("nested sums over rows are not supported")
+        self.partial[n.name] = bool(n.over_m) or self._check_partial(n)
+        self.declare(n.name, n.shape)
+        m = self.fused.get(src)
+        keep_r = bool(n.shape[0])
+        if red_c:
+            kept = t.R if keep_r else 1
+            chain = (t.C // 2) * (t.R if red_r else 1)
+        else:
+            kept = t.C // 2
+            chain = t.R
+        nacc = max(1, min(2 if red_c else 4, chain // 4))
+        while kept * nacc > 16 and nacc > 1:
+            nacc //= 2
+        w.open("")
+        w(f"frnn_pk acc2[{kept * nacc}];")
+        w("#pragma unroll")
+        w(f"for (int q = 0; q < {kept * nacc}; q++) acc2[q] = frnn_pk_make(0.0f, 0.0f);")
+        opened = 0
+        if ss[0]:
+            w("#pragma unroll")
+            w.open(f"for (int r = 0; r < {t.R}; r++)")
+            opened += 1
+        w("#pragma unroll")
+        w.open(f"for (int c = 0; c < {t.C}; c += 2)")
+        opened += 1
+        rs = "r" if ss[0] else "0"
+        if red_c:
+            kidx = "r" if keep_r else "0"
+            ridx = f"(r * {t.C // 2} + (c >> 1))" if red_r else "(c >> 1)"
+        else:
+            kidx, ridx = "(c >> 1)", "r"
+        acc = f"acc2[({kidx}) * {nacc} + ({ridx}) % {nacc}]"
+        if m is not None:
+            x, y = m.args
+            w(f"{acc} = frnn_fma2({self.pair(x, rs, 'c')}, {self.pair(y, rs, 'c')}, {acc});")
+        else:
+            w(f"{acc} = frnn_add2({acc}, {self.pair(src, rs, 'c')});")
+        for _ in range(opened):
+            w.close()
+        w("#pragma unroll")
+        w.open(f"for (int k = 0; k < {kept}; k++)")
+        tot = f"acc2[k * {nacc}]"
+        for q in range(1, nacc):
+            tot = f"frnn_add2({tot}, acc2[k * {nacc} + {q}])"
+        if nacc == 4:
+            tot = f"frnn_add2(frnn_add2(acc2[k * 4], acc2[k * 4 + 1]), frnn_add2(acc2[k * 4 + 2], acc2[k * 4 + 3]))"
+        w(f"const frnn_pk tot = {tot};")
+        if red_c:
+            w(f"{vname(n.name)}[k] = tot.x + tot.y;")
+        else:
+            w(f"{vname(n.name)}[2 * k] = tot.x; {vname(n.name)}[2 * k + 1] = tot.y;")
+        w.close()
+        if red_c and t.L > 1:
+            off = t.L // 2
+            while off > 0:
+                w("#pragma unroll")
+                w(f"for (int k = 0; k < {kept}; k++) {vname(n.name)}[k] += frnn_shfl_xor({vname(n.name)}[k], {off});")
+                off //= 2
+        w.close()
+        return True
+
+    def graph(self, g: StepGraph, allow_over_m: bool = False, keep: Iterable[str] = ()):
+        self.fuse_group(g.nodes, g.nodes, set(g.outputs) | set(keep))
         for n in g.nodes:
             self.node(n, allow_over_m)
 
@@ -1431,12 +1641,24 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.open("")
         sub = Body(w, t, body.shape)
         read_wk_inputs(sub, g_aux2)
-        sub.graph(g_aux2)
-        for k in range(ns):
-            o = g_aux2.outputs[k]
-            sgn = "-" if reverse.sign[k] > 0 else "+"
-            sub.loops(stcls, lambda r, c, k=k, o=o, sgn=sgn:
-                      f"{body.at(p.st_names[k], r, c)} = {body.at(p.st_names[k], r, c)} {sgn} {sub.at(o, r, c)};")
+        # the update of the state registers is written as one more node, so that the product
+        # that forms the increment folds into a packed multiply-add
+        upd = [Node(f"unstep{k}", "sub" if reverse.sign[k] > 0 else "add", [p.st_names[k], g_aux2.outputs[k]], stcls)
+               for k in range(ns)]
+        nodes = list(g_aux2.nodes) + upd
+        sub.fuse_group(nodes, nodes, ())
+        for n in g_aux2.nodes:
+            sub.node(n, False)
+        for k, u in enumerate(upd):
+            st = p.st_names[k]
+            if sub.can_pack() and sub.pair_expr(u, "r", "c") is not None:
+                sub.pair_loops(stcls, lambda r, c, u=u, st=st: (
+                    f"{{ const frnn_pk v2 = {sub.pair_expr(u, r, c)}; "
+                    f"{body.at(st, r, c)} = v2.x; {body.at(st, r, c + ' + 1')} = v2.y; }}"))
+            else:
+                sgn = "-" if u.op == "sub" else "+"
+                sub.loops(stcls, lambda r, c, st=st, u=u, sgn=sgn:
+                          f"{body.at(st, r, c)} = {body.at(st, r, c)} {sgn} {sub.at(u.args[1], r, c)};")
         w.close()
 
     def emit_bw_step():
@@ -1449,13 +1671,17 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 sub.alias[nm] = p.st_names[k]
                 sub.shape[nm] = stcls
             dep_cur = g_bw2.depends_on(p.st_names)
-            for n in g_bw2.nodes:
-                if n.name not in dep_cur:
-                    sub.node(n, True)
+            phase1 = [n for n in g_bw2.nodes if n.name not in dep_cur]
+            phase2 = [n for n in g_bw2.nodes if n.name in dep_cur]
+            # a product is only folded into a consumer of its own phase: between the phases the state
+            # registers change from S_{t+1} to S_t
+            sub.fuse_group(phase1, g_bw2.nodes, g_bw2.outputs)
+            for n in phase1:
+                sub.node(n, True)
             emit_unstep()
-            for n in g_bw2.nodes:
-                if n.name in dep_cur:
-                    sub.node(n, True)
+            sub.fuse_group(phase2, g_bw2.nodes, g_bw2.outputs)
+            for n in phase2:
+                sub.node(n, True)
         else:
             if rev:
                 emit_unstep()

@@ -93,6 +93,7 @@ class Tuning:
     bw_unroll: int = 4
     slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
     col_major: int = 0       # emit full-tile loops with columns outermost
+    pack2: int = 1           # packed fp32x2 arithmetic (two columns per instruction): bit 0 backward, bit 1 forward
     autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     use_tma: bool = True
@@ -325,6 +326,7 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None) -> lower.Ker
     """Emit the forward kernel (for ``tile`` instead of the planned tile if given)."""
     p, tu = plan.problem, plan.tuning
     lower.Body.col_major = bool(tu.col_major)
+    lower.Body.pack2 = bool(tu.pack2 & 2)
     tile = tile or plan.fw_tile
     # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
     stage = tu.fw_stage
@@ -362,6 +364,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
     only the flush parameters are re-fitted; None if it does not fit."""
     p, tu = plan.problem, plan.tuning
     lower.Body.col_major = bool(tu.col_major)
+    lower.Body.pack2 = bool(tu.pack2 & 1)
     sg, kflush, bufs = plan.bw_choice
     cands = [(kflush, bufs)]
     if tile is not None and tile is not plan.bw_tile:

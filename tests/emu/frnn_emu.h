@@ -134,6 +134,11 @@ FRNN_DEV void frnn_report(int* err, int code) { std::lock_guard<std::mutex> g(em
 FRNN_DEV float frnn_expf(float x) { return std::exp(x); }
 FRNN_DEV float frnn_logf(float x) { return std::log(x); }
 FRNN_DEV float frnn_sqrtf(float x) { return std::sqrt(x); }
+struct frnn_pk { float x, y; };
+FRNN_DEV frnn_pk frnn_pk_make(float a, float b) { return frnn_pk{a, b}; }
+FRNN_DEV frnn_pk frnn_fma2(frnn_pk a, frnn_pk b, frnn_pk c) { return frnn_pk{fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)}; }
+FRNN_DEV frnn_pk frnn_mul2(frnn_pk a, frnn_pk b) { return frnn_pk{a.x * b.x, a.y * b.y}; }
+FRNN_DEV frnn_pk frnn_add2(frnn_pk a, frnn_pk b) { return frnn_pk{a.x + b.x, a.y + b.y}; }
 FRNN_DEV float frnn_rcpf(float x) { return 1.0f / x; }
 FRNN_DEV float frnn_divf(float a, float b) { return a / b; }
 

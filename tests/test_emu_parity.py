@@ -41,6 +41,20 @@ def test_fp32_ragged_T(op):
     assert fwd.sources[0].info["tma_items"] > 0       # rows of 16 fp32 = 64 B go through the bulk-copy path
 
 
+@pytest.mark.parametrize("op", list(W.STEPS))
+@pytest.mark.parametrize("pack2", [0, 3])
+def test_packed_and_scalar_arithmetic(op, pack2):
+    """The scan loops written with two-column packed operations in both
+    kernels (products folded into packed fused multiply-adds), and without
+    them, give the same results."""
+    import dataclasses
+    xs, dy, dS = O.make_case(op, 1, 6, 2, 8, 16, torch.float32)
+    y, ST, grads, fwd = run_emu(op, xs, dy, dS, dataclasses.replace(SMALL, pack2=pack2))
+    check(op, xs, dy, dS, (y, ST, grads), 1e-5, 1e-5)
+    packed = ["frnn_fma2(" in ks.source.split('extern "C"')[-1] for ks in fwd.sources]
+    assert packed == [bool(pack2), bool(pack2)]
+
+
 @pytest.mark.parametrize("op,M,N,tu", [
     ("mamba2", 8, 16, Tuning(fw_r=1, fw_c=8, fw_mb=8, fw_stage=3, bw_r=1, bw_c=4, seg=3, nslots=1)),
     ("rwkv7", 16, 32, Tuning(fw_r=2, fw_c=8, fw_mb=16, fw_stage=8, bw_r=4, bw_c=8, seg=2, nslots=3)),
