@@ -160,6 +160,9 @@ template <int L> FRNN_DEV float frnn_row_sum(float v) {
 // the CNT elements are fetched with the widest access their size allows.  The
 // caller guarantees that element i sits on a CNT-element boundary of a
 // 16-byte aligned base.  Works on shared and global memory alike.
+#ifndef FRNN_ASSERT_ALIGNED     // the host emulation defines it to abort on an access the GPU would fault on
+#define FRNN_ASSERT_ALIGNED(p, n)
+#endif
 struct __align__(8) frnn_u2 { u32 x, y; };
 struct __align__(16) frnn_u4 { u32 x, y, z, w; };
 struct __align__(8) frnn_f2 { float x, y; };
@@ -177,22 +180,27 @@ template <> FRNN_DEV u32 frnn_pack16<2>(float a, float b) { return (u32)frnn_f32
 
 template <int DT, int CNT> FRNN_DEV void frnn_ldv(const void* base, long i, float* out) {
     if constexpr (DT == 0 && CNT == 4) {
+        FRNN_ASSERT_ALIGNED((const float*)base + i, 16);
         frnn_f4 t = *(const frnn_f4*)((const float*)base + i);
         out[0] = t.x; out[1] = t.y; out[2] = t.z; out[3] = t.w;
     } else if constexpr (DT == 0 && CNT == 2) {
+        FRNN_ASSERT_ALIGNED((const float*)base + i, 8);
         frnn_f2 t = *(const frnn_f2*)((const float*)base + i);
         out[0] = t.x; out[1] = t.y;
     } else if constexpr ((DT == 1 || DT == 2) && CNT == 8) {
+        FRNN_ASSERT_ALIGNED((const u16*)base + i, 16);
         frnn_u4 t = *(const frnn_u4*)((const u16*)base + i);
         out[0] = frnn_lo16<DT>(t.x); out[1] = frnn_hi16<DT>(t.x);
         out[2] = frnn_lo16<DT>(t.y); out[3] = frnn_hi16<DT>(t.y);
         out[4] = frnn_lo16<DT>(t.z); out[5] = frnn_hi16<DT>(t.z);
         out[6] = frnn_lo16<DT>(t.w); out[7] = frnn_hi16<DT>(t.w);
     } else if constexpr ((DT == 1 || DT == 2) && CNT == 4) {
+        FRNN_ASSERT_ALIGNED((const u16*)base + i, 8);
         frnn_u2 t = *(const frnn_u2*)((const u16*)base + i);
         out[0] = frnn_lo16<DT>(t.x); out[1] = frnn_hi16<DT>(t.x);
         out[2] = frnn_lo16<DT>(t.y); out[3] = frnn_hi16<DT>(t.y);
     } else if constexpr ((DT == 1 || DT == 2) && CNT == 2) {
+        FRNN_ASSERT_ALIGNED((const u16*)base + i, 4);
         u32 t = *(const u32*)((const u16*)base + i);
         out[0] = frnn_lo16<DT>(t); out[1] = frnn_hi16<DT>(t);
     } else {
@@ -204,20 +212,25 @@ template <int DT, int CNT> FRNN_DEV void frnn_ldv(const void* base, long i, floa
 template <int DT, int CNT> FRNN_DEV void frnn_stv(void* base, long i, const float* v) {
     if constexpr (DT == 0 && CNT == 4) {
         frnn_f4 t; t.x = v[0]; t.y = v[1]; t.z = v[2]; t.w = v[3];
+        FRNN_ASSERT_ALIGNED((float*)base + i, 16);
         *(frnn_f4*)((float*)base + i) = t;
     } else if constexpr (DT == 0 && CNT == 2) {
         frnn_f2 t; t.x = v[0]; t.y = v[1];
+        FRNN_ASSERT_ALIGNED((float*)base + i, 8);
         *(frnn_f2*)((float*)base + i) = t;
     } else if constexpr ((DT == 1 || DT == 2) && CNT == 8) {
         frnn_u4 t;
         t.x = frnn_pack16<DT>(v[0], v[1]); t.y = frnn_pack16<DT>(v[2], v[3]);
         t.z = frnn_pack16<DT>(v[4], v[5]); t.w = frnn_pack16<DT>(v[6], v[7]);
+        FRNN_ASSERT_ALIGNED((u16*)base + i, 16);
         *(frnn_u4*)((u16*)base + i) = t;
     } else if constexpr ((DT == 1 || DT == 2) && CNT == 4) {
         frnn_u2 t;
         t.x = frnn_pack16<DT>(v[0], v[1]); t.y = frnn_pack16<DT>(v[2], v[3]);
+        FRNN_ASSERT_ALIGNED((u16*)base + i, 8);
         *(frnn_u2*)((u16*)base + i) = t;
     } else if constexpr ((DT == 1 || DT == 2) && CNT == 2) {
+        FRNN_ASSERT_ALIGNED((u16*)base + i, 4);
         *(u32*)((u16*)base + i) = frnn_pack16<DT>(v[0], v[1]);
     } else {
 #pragma unroll

@@ -30,6 +30,8 @@ using std::max;
 #define __restrict__
 #define __launch_bounds__(...)
 #define __align__(n) alignas(n)
+// a vector access that is not aligned to its own size faults on the GPU ("misaligned address"); abort here instead
+#define FRNN_ASSERT_ALIGNED(p, n) do { if (((uintptr_t)(p)) % (n)) { fprintf(stderr, "emu: misaligned %d-byte access at %p\n", (int)(n), (const void*)(p)); abort(); } } while (0)
 
 struct emu_dim3 { unsigned x = 0, y = 0, z = 0; };
 struct emu_cta {
