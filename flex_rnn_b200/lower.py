@@ -742,6 +742,8 @@ class KernelBuilder:
         return the graphs rewritten to read those values as inputs."""
         off = 0
         for it in sorted(self.items, key=lambda i: not i.tma):
+            if it.tma and it.tmap:
+                off = (off + 127) // 128 * 128     # a tiled tensor copy needs a 128-byte aligned destination
             it.off = off
             off += it.rowb * self.D
         self.stage_bytes = (off + 127) // 128 * 128

@@ -95,7 +95,8 @@ struct alignas(64) frnn_tmap {
 static_assert(sizeof(frnn_tmap) == 128, "tensor map emulation must be 128 bytes");
 #define FRNN_TMAP_PARAM const frnn_tmap
 FRNN_DEV void frnn_tma_load_4d(void* dst, const frnn_tmap* m, int c0, int c1, int c2, int c3, u64* bar) {
-    if (((uintptr_t)dst & 15) || ((long)c0 * m->elt) % 16) { fprintf(stderr, "emu: misaligned tensor load\n"); abort(); }
+    // a tiled tensor copy wants its shared-memory destination on a 128-byte boundary and the innermost coordinate on 16 bytes
+    if (((uintptr_t)dst & 127) || ((long)c0 * m->elt) % 16) { fprintf(stderr, "emu: misaligned tensor load\n"); abort(); }
     unsigned char* d = (unsigned char*)dst;
     size_t total = 0;
     for (u32 w3 = 0; w3 < m->box[3]; w3++)
