@@ -118,13 +118,41 @@ def draw_case(rng: random.Random):
     return fam, step, ins, sts, dtype, tu
 
 
-@pytest.mark.parametrize("seed", range(2000, 2014))
+def on_device(x, dev):
+    """Copy to ``dev`` keeping the strides and the storage offset modulo 16 bytes."""
+    if dev is None:
+        return x
+    span = 1 + sum((n - 1) * st for n, st in zip(x.shape, x.stride()))
+    lead = x.storage_offset() % (16 // x.element_size())
+    buf = torch.zeros(lead + span, dtype=x.dtype, device=dev)
+    out = buf.as_strided(x.shape, x.stride(), lead)
+    out.copy_(x)
+    return out
+
+
+SEEDS = range(2000, 2014)
+
+
+@pytest.mark.parametrize("seed", SEEDS)
 def test_random_case(seed):
     from emu.emu import EmuLauncher
+    run_case(seed, None, EmuLauncher)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", SEEDS)
+def test_random_case_gpu(seed):
+    """The same seeds through NVRTC and the C-ABI launch on the GPU (each has
+    passed the emulation's alignment checks in the CPU test)."""
+    run_case(seed, "cuda:0", None)
+
+
+def run_case(seed, dev, launcher):
     rng = random.Random(seed)
     fam, step, ins, sts, dtype, tu = draw_case(rng)
+    ins, sts = [on_device(x, dev) for x in ins], [on_device(x, dev) for x in sts]
     try:
-        fwd, bwd, _, _ = build_twopass(step, tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
+        fwd, bwd, _, _ = build_twopass(step, tuple(ins), tuple(sts), tuning=tu, _launcher=launcher)
     except lower.LoweringError as e:
         pytest.skip(f"{fam}: {e}")
     res = fwd(tuple(ins), tuple(sts))
@@ -133,7 +161,13 @@ def test_random_case(seed):
     g = torch.Generator().manual_seed(seed)
     dys = [torch.randn(y.shape, generator=g).to(dtype) for y in res[:no]]
     dSs = [torch.randn(s.shape, generator=g).to(dtype) for s in sts]
-    dx, ds0 = bwd(tuple(dys), tuple(dSs), tuple(ins), tuple(res[no + ns:no + 2 * ns]), (res[-1],))
+    dx, ds0 = bwd(tuple(d.to(ins[0].device) for d in dys), tuple(d.to(ins[0].device) for d in dSs), tuple(ins),
+                  tuple(res[no + ns:no + 2 * ns]), (res[-1],))
+    if dev is not None:
+        torch.cuda.synchronize()
+        assert fwd.kernel_status(dev) == 0
+        res, dx, ds0 = [r.cpu() for r in res], [d.cpu() for d in dx], [d.cpu() for d in ds0]
+        ins, sts = [x.cpu() for x in ins], [x.cpu() for x in sts]
     ry, rST, rgx, rgs = O.fwd_bwd(step, ins, sts, dys, dSs, dtype=torch.float64)
     tol_out, tol_grad = (1e-5, 3e-5) if dtype == torch.float32 else (8e-3, 2e-2)
     got = list(res[:no + ns]) + list(dx) + list(ds0)
