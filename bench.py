@@ -407,9 +407,10 @@ def main():
                        "l2": f"no flush: each step streams {stream_mb:.0f} MB of inputs, outputs, checkpoints and row sums "
                              "through HBM (L2 is 126 MB)",
                        "checkpoint_every": plan.D, "backward": "reverse re-step" if plan.reverse else "recompute from slots",
-                       "fw_kernel": {"grid": list(fw_src.grid), "block": fw_src.block, "smem": fw_src.smem_bytes},
+                       "fw_kernel": {"grid": list(fw_src.grid), "block": fw_src.block, "smem": fw_src.smem_bytes,
+                                     "tile": fw_src.info["tile"][:2], "packed_fp32x2": fw_src.info["packed"]},
                        "bw_kernel": {"grid": list(bw_src.grid), "block": bw_src.block, "smem": bw_src.smem_bytes,
-                                     "tile": [plan.bw_tile.R, plan.bw_tile.C]}},
+                                     "tile": bw_src.info["tile"][:2], "packed_fp32x2": bw_src.info["packed"]}},
             "fw_ms": fw_avg, "bw_ms": bw_avg,
             "roofline_fraction_step": max(t_fp32, t_hbm) / (ms_per_step * 1e-3),
             "roofline": {"bound": "fp32", "kernel": bw_src.name, "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",

@@ -1277,7 +1277,8 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     w.close()
     return KernelSource(kname, w.text(), (p.M // t.MB, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "tma_items": len(kb.tma_items),
-                         "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted]},
+                         "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted],
+                         "tile": [t.R, t.C, t.MB], "packed": Body.pack2},
                         kb.tmaps)
 
 
@@ -1872,4 +1873,5 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
-                         "reverse": rev, "hoisted": [n.name for n in kb.hoisted]}, kb.tmaps)
+                         "reverse": rev, "hoisted": [n.name for n in kb.hoisted], "tile": [t.R, t.C, t.MB],
+                         "packed": Body.pack2}, kb.tmaps)

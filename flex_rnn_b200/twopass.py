@@ -325,11 +325,12 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     return plan, fw_meta, bw_meta
 
 
-def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None) -> lower.KernelSource:
-    """Emit the forward kernel (for ``tile`` instead of the planned tile if given)."""
+def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Optional[bool] = None) -> lower.KernelSource:
+    """Emit the forward kernel (for ``tile`` instead of the planned tile, with
+    packed arithmetic switched as ``pack`` instead of the tuning's choice, if given)."""
     p, tu = plan.problem, plan.tuning
     lower.Body.col_major = bool(tu.col_major)
-    lower.Body.pack2 = bool(tu.pack2 & 2)
+    lower.Body.pack2 = bool(tu.pack2 & 2) if pack is None else bool(pack)
     tile = tile or plan.fw_tile
     # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
     stage = tu.fw_stage
@@ -640,10 +641,13 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         forward kernel only writes its outputs) and keep the fastest."""
         tuned["fw"] = True
         best = None
-        for tile in forward_tile_candidates(plan):
+        default_pack = bool(plan.tuning.pack2 & 2)
+        cands = [(tile, default_pack) for tile in forward_tile_candidates(plan)] + [(plan.fw_tile, not default_pack)]
+        for tile, pack in cands:
             try:
-                ks = fw_src if tile is plan.fw_tile else generate_forward(plan, tile)
-                launcher = launch_fw if tile is plan.fw_tile else make(ks)
+                planned = tile is plan.fw_tile and pack == default_pack
+                ks = fw_src if planned else generate_forward(plan, tile, pack)
+                launcher = launch_fw if planned else make(ks)
                 launcher(ptrs, device)                                   # compile + warm up
                 ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
                 ev[0].record()
