@@ -49,8 +49,8 @@ WORKLOADS = {
     "gated_delta_rule": ("gated_delta_rule", 8, 1024, 32, 128, 128),
 }
 # DRAM bytes (read + write) of one backward launch per (batch, head) pair, from the ncu capture summarised in
-# profiles/delta_rule_b2_frnn_fw_bw_ncu_full.md (B=2: 202.9 MB over 64 pairs); traffic grows with the pair count
-NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 202.9e6 / 64}
+# profiles/delta_rule_b2_frnn_fw_bw_ncu_full.md (B=2: 204.0 MB over 64 pairs); traffic grows with the pair count
+NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 204.03e6 / 64, "rwkv7": 782.1e6 / 64}
 METRIC = "fwd+bwd tokens/s"
 UNIT = "tokens/s"
 
@@ -100,13 +100,14 @@ def bytes_io(tensors):
     return sum(t.numel() * t.element_size() for t in tensors)
 
 
-def cpu_sample(opname, B, T, H, M, N, seconds_hint=15.0):
+def cpu_sample(opname, B, T, H, M, N, heads=None):
     """Times the CPU oracle (fwd + autograd bwd) on a (b,h) sub-slice of the
     workload and scales to whole-workload tokens/s (the slices are independent
-    recurrences of equal cost)."""
+    recurrences of equal cost).  ``heads``: heads of one batch element in the
+    sample (default: all of them, about ten seconds of CPU work)."""
     import torch
     from oracle import naive_oracle as O
-    sb, sh = 1, min(H, 4)
+    sb, sh = 1, min(H, heads or H)
     xs, dy, dS = O.make_case(opname, sb, T, sh, M, N, torch.bfloat16)
     t0 = time.perf_counter()
     O.fwd_bwd(O.STEPS[opname], xs[:-1], xs[-1:], [dy], [dS])
@@ -122,13 +123,16 @@ def run_reference(args, rank, world):
         return
     import torch
     opname, B, T, H, M, N = WORKLOADS[args.op]
+    # size the per-step sample so that the whole run stays within a few minutes (about 0.25 s per head)
+    n = max(1, args.warmup + args.steps)
+    heads = next((h for h in (32, 16, 8, 4, 2, 1) if h <= H and 0.25 * h * n <= 150), 1)
     times = []
     base = None
     for i in range(args.warmup + args.steps):
-        base, dt = cpu_sample(opname, B, T, H, M, N)
+        base, dt = cpu_sample(opname, B, T, H, M, N, heads)
         if i >= args.warmup:
             times.append(dt)
-    frac = (1 * min(H, 4)) / (B * H)
+    frac = (1 * min(H, heads)) / (B * H)
     ms = 1e3 * sum(times) / len(times)
     value = B * T * frac / (ms / 1e3)
     base["value"] = value
@@ -427,7 +431,14 @@ def main():
             "clocks": clocks,
         }
         if not args.no_cpu_baseline:
-            line["cpu_baseline"], _ = cpu_sample(opname, B, T, H, M, N)
+            # one cold pass, then the mean of three (about ten seconds of CPU work on all host threads)
+            cpu_sample(opname, B, T, H, M, N)
+            runs = [cpu_sample(opname, B, T, H, M, N) for _ in range(3)]
+            base = runs[-1][0]
+            mean_dt = sum(dt for _, dt in runs) / len(runs)
+            base["value"] = base["value"] * runs[-1][1] / mean_dt
+            base["sample"] += f"; mean of 3 passes after one cold pass ({mean_dt:.2f} s each)"
+            line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
