@@ -3,7 +3,8 @@ emulation of the generated kernels and checked against the naive scan in fp64.
 
 Each seed draws a step family, state sizes (including one-row, one-column,
 1x1 and non-power-of-two states), B/T/H (T not a multiple of any stage
-length), broadcasting over batch / time / heads, I/O dtype, memory layouts
+length), broadcasting over batch / time / heads, I/O dtype (fp32, bf16, fp16,
+fp64; the arithmetic is fp32 throughout), memory layouts
 (strided last dimension, odd storage offsets, time-major inputs, transposed
 states) and tiling parameters.  The emulation aborts on any vector access or
 bulk copy that the GPU would reject as misaligned, so a pass also means that
@@ -84,7 +85,7 @@ def draw_case(rng: random.Random):
             s = list(ins[0].shape)
             s[d] = full
             ins[0] = ins[0].expand(*s).contiguous()
-    dtype = rng.choice([torch.float32, torch.float32, torch.bfloat16])
+    dtype = rng.choice([torch.float32, torch.float32, torch.bfloat16, torch.bfloat16, torch.float16, torch.float64])
     ins, sts = [x.to(dtype) for x in ins], [x.to(dtype) for x in sts]
     # layouts
     if rng.random() < 0.3:                        # every second element of a wider last dimension
@@ -130,7 +131,7 @@ def on_device(x, dev):
     return out
 
 
-SEEDS = range(2000, 2014)
+SEEDS = range(2000, 2016)
 
 
 @pytest.mark.parametrize("seed", SEEDS)
@@ -169,7 +170,7 @@ def run_case(seed, dev, launcher):
         res, dx, ds0 = [r.cpu() for r in res], [d.cpu() for d in dx], [d.cpu() for d in ds0]
         ins, sts = [x.cpu() for x in ins], [x.cpu() for x in sts]
     ry, rST, rgx, rgs = O.fwd_bwd(step, ins, sts, dys, dSs, dtype=torch.float64)
-    tol_out, tol_grad = (1e-5, 3e-5) if dtype == torch.float32 else (8e-3, 2e-2)
+    tol_out, tol_grad = (1e-5, 3e-5) if dtype in (torch.float32, torch.float64) else (8e-3, 2e-2)
     got = list(res[:no + ns]) + list(dx) + list(ds0)
     want = list(ry) + list(rST) + rgx + rgs
     for k, (a, b, like) in enumerate(zip(got, want, [None] * (no + ns) + ins + sts)):
@@ -177,7 +178,7 @@ def run_case(seed, dev, launcher):
         assert a.shape == b.shape, (fam, k)
         if like is not None:
             assert a.dtype == like.dtype
-        if b.numel() < 16 and dtype != torch.float32:
+        if b.numel() < 16 and dtype in (torch.bfloat16, torch.float16):
             continue                              # a handful of bf16 values: one rounding step dominates the norm
         err = O.rel_err(a, b) if float(b.abs().max()) > 0 else float(a.float().abs().max())
         assert err < (tol_out if k < no + ns else tol_grad), (fam, k, err, tu)
