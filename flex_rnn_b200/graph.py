@@ -31,7 +31,7 @@ S11: Shape = (0, 0)
 
 #: elementwise ops with one tensor operand
 UNARY = ("neg", "exp", "log", "sqrt", "rsqrt", "reciprocal", "abs", "sigmoid",
-         "tanh", "copy", "log1p", "expm1", "relu", "sign")
+         "tanh", "copy", "log1p", "expm1", "relu", "sign", "erf")
 #: elementwise ops with two operands (either may be a literal)
 BINARY = ("mul", "add", "sub", "div", "gt", "lt", "ge", "le", "eq", "ne",
           "maximum", "minimum", "pow")
@@ -127,12 +127,13 @@ class StepGraph:
 _ATEN_UNARY = {
     "neg": "neg", "exp": "exp", "log": "log", "sqrt": "sqrt", "rsqrt": "rsqrt",
     "reciprocal": "reciprocal", "abs": "abs", "sigmoid": "sigmoid", "tanh": "tanh",
-    "log1p": "log1p", "expm1": "expm1", "relu": "relu", "sign": "sign", "sgn": "sign",
+    "log1p": "log1p", "expm1": "expm1", "relu": "relu", "sign": "sign", "sgn": "sign", "erf": "erf",
 }
 _ATEN_BINARY = {
     "mul": "mul", "add": "add", "sub": "sub", "div": "div", "gt": "gt", "lt": "lt",
     "ge": "ge", "le": "le", "eq": "eq", "ne": "ne", "maximum": "maximum",
-    "minimum": "minimum", "pow": "pow",
+    "minimum": "minimum", "pow": "pow", "clamp_min": "maximum", "clamp_max": "minimum",
+    "logical_and": "mul", "bitwise_and": "mul",      # operands are 0/1 masks here
 }
 _ATEN_ALIAS = ("clone", "_to_copy", "expand", "alias", "detach", "lift_fresh_copy",
                "contiguous", "to", "view", "_unsafe_view", "reshape")
@@ -202,6 +203,11 @@ def from_fx(gm: torch.fx.GraphModule, name: str, dims: Tuple[int, int]) -> StepG
         base = tname.split(".")[0]
         val = fx.meta.get("val")
         shp = cls(val) if val is not None else S11
+        # an in-place form (autograd formulas use a few: fill_, sub_, logical_and_) is imported as the
+        # out-of-place operation, and later readers of the overwritten tensor are pointed at the result
+        mutated = None
+        if base.endswith("_") and (base[:-1] in _ATEN_UNARY or base[:-1] in _ATEN_BINARY or base[:-1] == "fill"):
+            mutated, base = fx.args[0], base[:-1]
         if base in _ATEN_ALIAS:
             src = res(fx.args[0])
             if isinstance(src, str) and val is not None and base in ("view", "_unsafe_view", "reshape"):
@@ -242,9 +248,29 @@ def from_fx(gm: torch.fx.GraphModule, name: str, dims: Tuple[int, int]) -> StepG
                 alias[fx.name] = src
                 continue
             emit(fx.name, "sum", [src], (ss[0] * (not om), ss[1] * (not on)), over_m=om, over_n=on)
-        elif base in ("ones_like", "zeros_like", "full_like", "full", "zeros", "ones",
-                      "scalar_tensor", "new_zeros", "new_ones", "new_full"):
-            if base in ("zeros_like", "zeros", "new_zeros"):
+        elif base == "mean":
+            src = res(fx.args[0])
+            dims_ = list(fx.args[1]) if len(fx.args) > 1 and fx.args[1] is not None else [0, 1]
+            keep = bool(fx.args[2]) if len(fx.args) > 2 else bool(fx.kwargs.get("keepdim", False))
+            if not isinstance(src, str) or (not keep and len(tuple(val.shape)) != 0):
+                raise UnsupportedStepOp("only mean(..., keepdim=True) keeps the per-head 2-D form")
+            full = tuple(fx.args[0].meta["val"].shape)
+            dims_ = sorted({d % 2 for d in dims_})
+            count = 1
+            for d in dims_:
+                count *= full[d]
+            ss = shape[src]
+            om, on = (0 in dims_) and bool(ss[0]), (1 in dims_) and bool(ss[1])
+            cur = src
+            if om or on:
+                emit(fx.name + "_sum", "sum", [src], (ss[0] * (not om), ss[1] * (not on)), over_m=om, over_n=on)
+                cur = fx.name + "_sum"
+            # a broadcast dimension counts in the mean's divisor but not in the sum
+            kept = (full[0] if (0 in dims_ and not om) else 1) * (full[1] if (1 in dims_ and not on) else 1)
+            emit(fx.name, "mul", [cur, float(kept) / float(count)], shape[cur])
+        elif base in ("ones_like", "zeros_like", "full_like", "full", "zeros", "ones", "fill", "empty_like", "empty",
+                      "scalar_tensor", "new_zeros", "new_ones", "new_full", "new_empty"):
+            if base in ("zeros_like", "zeros", "new_zeros", "empty_like", "empty", "new_empty"):
                 c = 0.0
             elif base in ("ones_like", "ones", "new_ones"):
                 c = 1.0
@@ -271,9 +297,108 @@ def from_fx(gm: torch.fx.GraphModule, name: str, dims: Tuple[int, int]) -> StepG
             emit(t0, "mul", [y, y], ys)
             emit(t1, "sub", [1.0, t0], ys)
             emit(fx.name, "mul", [g, t1], shp)
+        elif base == "threshold_backward":   # grad * (x > threshold)
+            g, x, thr = res(fx.args[0]), res(fx.args[1]), float(fx.args[2])
+            xs = shape[x] if isinstance(x, str) else S11
+            emit(fx.name + "_m", "gt", [x, thr], xs)
+            emit(fx.name, "mul", [g, fx.name + "_m"], shp)
+        elif base == "clamp":                # max(min(x, hi), lo)
+            x = res(fx.args[0])
+            lo = fx.args[1] if len(fx.args) > 1 else fx.kwargs.get("min")
+            hi = fx.args[2] if len(fx.args) > 2 else fx.kwargs.get("max")
+            cur = x
+            if lo is not None:
+                emit(fx.name + "_lo", "maximum", [cur, res(lo)], shp)
+                cur = fx.name + "_lo"
+            if hi is not None:
+                emit(fx.name + "_hi", "minimum", [cur, res(hi)], shp)
+                cur = fx.name + "_hi"
+            alias[fx.name] = cur
+        elif base in ("masked_fill", "masked_fill_"):   # where(mask, value, x)
+            x, m, v = res(fx.args[0]), res(fx.args[1]), res(fx.args[2])
+            emit(fx.name, "where", [m, v, x], shp)
+            if base.endswith("_") and isinstance(fx.args[0], torch.fx.Node):
+                alias[fx.args[0].name] = fx.name        # later readers of the mutated tensor see the new value
+        elif base in ("elu", "elu_backward"):
+            t = lambda k: f"{fx.name}_{k}"
+            if base == "elu":
+                x, rest = res(fx.args[0]), list(fx.args[1:])
+            else:
+                if bool(fx.args[4]):
+                    raise UnsupportedStepOp("elu_backward on the result is not supported")
+                x, rest = res(fx.args[5]), list(fx.args[1:4])
+            alpha, scale, iscale = [float(v) for v in rest + [1.0, 1.0, 1.0][len(rest):]]
+            xs = shape[x] if isinstance(x, str) else S11
+            emit(t("p"), "gt", [x, 0.0], xs)
+            emit(t("z"), "mul", [x, iscale], xs)
+            emit(t("e"), "exp", [t("z")], xs)
+            if base == "elu":                  # scale * (x > 0 ? x : alpha * (exp(input_scale x) - 1))
+                emit(t("m"), "sub", [t("e"), 1.0], xs)
+                emit(t("a"), "mul", [t("m"), alpha], xs)
+                emit(t("w"), "where", [t("p"), x, t("a")], xs)
+                emit(fx.name, "mul", [t("w"), scale], shp)
+            else:                              # grad * scale * (x > 0 ? 1 : alpha * input_scale * exp(input_scale x))
+                emit(t("a"), "mul", [t("e"), alpha * iscale], xs)
+                emit(t("w"), "where", [t("p"), 1.0, t("a")], xs)
+                emit(t("s"), "mul", [t("w"), scale], xs)
+                emit(fx.name, "mul", [res(fx.args[0]), t("s")], shp)
+        elif base == "logical_not":
+            emit(fx.name, "sub", [1.0, res(fx.args[0])], shp)
+        elif base in ("silu", "silu_backward", "softplus", "softplus_backward", "gelu", "gelu_backward"):
+            grad = res(fx.args[0]) if base.endswith("_backward") else None
+            x = res(fx.args[1] if grad is not None else fx.args[0])
+            xs = shape[x] if isinstance(x, str) else S11
+            t = lambda k: f"{fx.name}_{k}"
+            if base.startswith("silu"):
+                emit(t("s"), "sigmoid", [x], xs)
+                if grad is None:
+                    emit(fx.name, "mul", [x, t("s")], shp)
+                else:                        # s * (1 + x * (1 - s))
+                    emit(t("a"), "sub", [1.0, t("s")], xs)
+                    emit(t("b"), "mul", [x, t("a")], xs)
+                    emit(t("c"), "add", [t("b"), 1.0], xs)
+                    emit(t("d"), "mul", [t("s"), t("c")], xs)
+                    emit(fx.name, "mul", [grad, t("d")], shp)
+            elif base.startswith("softplus"):
+                rest = fx.args[2:] if grad is not None else fx.args[1:]
+                beta = float(rest[0]) if len(rest) > 0 else float(fx.kwargs.get("beta", 1.0))
+                thr = float(rest[1]) if len(rest) > 1 else float(fx.kwargs.get("threshold", 20.0))
+                emit(t("z"), "mul", [x, beta], xs)
+                emit(t("big"), "gt", [t("z"), thr], xs)
+                if grad is None:             # log1p(exp(beta x)) / beta, x itself above the threshold
+                    emit(t("zc"), "minimum", [t("z"), thr], xs)
+                    emit(t("e"), "exp", [t("zc")], xs)
+                    emit(t("l"), "log1p", [t("e")], xs)
+                    emit(t("v"), "mul", [t("l"), 1.0 / beta], xs)
+                    emit(fx.name, "where", [t("big"), x, t("v")], shp)
+                else:
+                    emit(t("s"), "sigmoid", [t("z")], xs)
+                    emit(t("w"), "where", [t("big"), 1.0, t("s")], xs)
+                    emit(fx.name, "mul", [grad, t("w")], shp)
+            else:
+                approx = fx.kwargs.get("approximate", "none")
+                if approx != "none":
+                    raise UnsupportedStepOp("gelu(approximate='tanh') is not supported inside a step function")
+                emit(t("u"), "mul", [x, 0.7071067811865476], xs)
+                emit(t("e"), "erf", [t("u")], xs)
+                emit(t("c"), "add", [t("e"), 1.0], xs)
+                emit(t("h"), "mul", [t("c"), 0.5], xs)             # Phi(x)
+                if grad is None:
+                    emit(fx.name, "mul", [x, t("h")], shp)
+                else:                        # Phi(x) + x * phi(x)
+                    emit(t("x2"), "mul", [x, x], xs)
+                    emit(t("n"), "mul", [t("x2"), -0.5], xs)
+                    emit(t("p"), "exp", [t("n")], xs)
+                    emit(t("q"), "mul", [t("p"), 0.3989422804014327], xs)
+                    emit(t("r"), "mul", [x, t("q")], xs)
+                    emit(t("d"), "add", [t("h"), t("r")], xs)
+                    emit(fx.name, "mul", [grad, t("d")], shp)
         else:
             raise UnsupportedStepOp(
                 f"operation aten.{tname} is not supported inside a step function "
-                "(supported: + - * / < > exp log sqrt and sum(-1, keepdim=True))")
+                "(supported: + - * / comparisons, where, exp log sqrt tanh sigmoid relu silu softplus gelu erf "
+                "abs sign clamp maximum minimum pow, and sum(-1, keepdim=True))")
+        if mutated is not None and isinstance(mutated, torch.fx.Node):
+            alias[mutated.name] = alias.get(fx.name, fx.name)
     g = StepGraph(name, inputs, nodes, outputs, shape)
     return g

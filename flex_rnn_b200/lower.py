@@ -224,6 +224,8 @@ def op_expr(n: Node, a: List[str]) -> str:
         return f"frnn_rcpf(frnn_sqrtf({a[0]}))"
     if op == "reciprocal":
         return f"frnn_rcpf({a[0]})"
+    if op == "erf":
+        return f"erff({a[0]})"
     if op == "abs":
         return f"fabsf({a[0]})"
     if op == "sigmoid":

@@ -56,14 +56,20 @@ def run_isolated(fn, *args):
 
 
 def trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: int,
-                has_m: bool = True, has_n: bool = True) -> Tuple[StepGraph, int, int]:
+                has_m: bool = True, has_n: bool = True,
+                dims: Tuple[int, int] = (TRACE_M, TRACE_N)) -> Tuple[StepGraph, int, int]:
     with clean_dispatch():
-        return _trace_joint(step, classes, n_inputs, has_m, has_n)
+        return _trace_joint(step, classes, n_inputs, has_m, has_n, dims)
 
 
 def _trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: int,
-                 has_m: bool = True, has_n: bool = True) -> Tuple[StepGraph, int, int]:
-    """Trace ``step`` on per-head tiles.
+                 has_m: bool = True, has_n: bool = True,
+                 dims: Tuple[int, int] = (TRACE_M, TRACE_N)) -> Tuple[StepGraph, int, int]:
+    """Trace ``step`` on per-head tiles of ``dims`` = (rows, columns).
+
+    The planner passes the real state size, as the reference does
+    (flex_rnn/twopass.py:86-90), so that a step function that reads a size
+    (``S.shape[-1] ** -0.5``) gets the constant it would get from ``naive``.
 
     ``classes[i]`` is ``(over_m, over_n)`` of argument ``i`` (inputs first, then
     states).  Returns the joint graph whose inputs are
@@ -71,8 +77,8 @@ def _trace_joint(step: Callable, classes: Sequence[Tuple[int, int]], n_inputs: i
     ``[*outputs, *new_states, *d_args]``, together with the number of outputs
     and of states.
     """
-    tm = TRACE_M if has_m else 1
-    tn = TRACE_N if has_n else 1
+    tm = max(2, dims[0]) if has_m else 1
+    tn = max(2, dims[1]) if has_n else 1
     if True:
         args = tuple(torch.empty(tm if c[0] else 1, tn if c[1] else 1, device="meta") for c in classes)
         counts: List[int] = []

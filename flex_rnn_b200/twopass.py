@@ -196,7 +196,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
 
     in_cls = [(int(x.shape[3] > 1), int(x.shape[4] > 1)) for x in inputs]
     st_cls = (int(M > 1), int(N > 1))
-    joint, no2, ns2 = trace_joint(step, in_cls + [st_cls] * nst, nin, has_m=M > 1, has_n=N > 1)
+    joint, no2, ns2 = trace_joint(step, in_cls + [st_cls] * nst, nin, has_m=M > 1, has_n=N > 1, dims=(M, N))
     assert (no2, ns2) == (nout, nst)
     jin = joint.inputs
     in_names, st_names = jin[:nin], jin[nin:nin + nst]

@@ -147,3 +147,25 @@ def test_tile_chooser():
     assert t.C == 1 and t.L == 1 and t.NT % 32 == 0
     with pytest.raises(LoweringError):
         choose_tile(4, 4, 1, 1)
+
+
+def test_sizes_read_inside_the_step_are_the_real_ones():
+    """A step that scales by its state's width must see the real width (the
+    reference traces on the real per-head sizes, twopass.py:86-90)."""
+    from emu.emu import EmuLauncher
+    from flex_rnn_b200.twopass import Tuning, build_twopass
+    from oracle import naive_oracle as O
+
+    def step(q, k, v, S):
+        S = S * 0.9 + v * k
+        return (S * q).sum(-1, True) * S.shape[-1] ** -0.5 + S.shape[-2], S
+
+    g = torch.Generator().manual_seed(0)
+    n = lambda *s: torch.randn(*s, generator=g)
+    B, T, H, M, N = 1, 5, 2, 8, 16
+    ins, sts = (n(B, T, H, 1, N), n(B, T, H, 1, N), n(B, T, H, M, 1)), (n(B, H, M, N),)
+    tu = Tuning(fw_r=2, fw_c=4, fw_mb=8, fw_stage=4, bw_r=2, bw_c=4, seg=2, nslots=2)
+    fwd, _, _, _ = build_twopass(step, ins, sts, tuning=tu, _launcher=EmuLauncher)
+    y = fwd(ins, sts)[0]
+    ry, _, _, _ = O.fwd_bwd(step, list(ins), list(sts), [torch.zeros_like(y)], [torch.zeros_like(sts[0])], dtype=torch.float64)
+    assert O.rel_err(y, ry[0]) < 1e-5

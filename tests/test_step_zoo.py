@@ -201,3 +201,103 @@ def test_gpu_pipelines(name):
     for a, b in zip(list(outs) + list(grads), list(ref_outs) + list(ref_grads)):
         assert a.shape == b.shape
         assert O.rel_err(a, b) < 5e-5, (name, O.rel_err(a, b))
+
+
+# ---- operations beyond the reference's table (+ - * / < > exp log sqrt, to_cuda.py:41-42) ----
+
+def _op_relu_mask(q, k, v, w, S):
+    S = S * torch.exp(-torch.relu(w)) + v * k * (k > 0)
+    return (S * q).sum(-1, True), S
+
+
+def _op_normalise(q, k, v, S):
+    S = S + v * k
+    S = S / (1 + (S * S).sum(-1, True))
+    return torch.log1p((S * q).sum(-1, True) ** 2), S
+
+
+def _op_maximum(q, k, v, w, S):
+    S = torch.maximum(S * torch.sigmoid(w), v * k)
+    return (S * q).sum(-1, True), S
+
+
+def _op_silu(q, k, v, S):
+    S = S * 0.5 + torch.nn.functional.silu(v * k)
+    return (S * q).sum(-1, True), S
+
+
+def _op_sign_clamp(q, k, v, S):
+    S = S - 0.1 * torch.sign(S) + v * k
+    return (S * q).sum(-1, True).clamp(-2, 2), S
+
+
+def _op_minimum_reciprocal(q, k, v, S):
+    S = torch.minimum(S * 0.9 + v * k, torch.ones_like(S) * 2)
+    return (S * q).sum(-1, True).exp().reciprocal(), S
+
+
+def _op_mean(q, k, v, S):
+    S = S * 0.9 + v * k
+    return (S * q).sum(-1, True) - (S * q).mean(-1, True), S
+
+
+def _op_softplus_where(q, k, v, S):
+    S = torch.where(S > 1, S * 0.5, S) + torch.nn.functional.softplus(v * k)
+    return torch.sqrt(torch.abs((S * q).sum(-1, True)) + 1), S
+
+
+def _op_gelu_elu(q, k, v, S):
+    S = S * 0.9 + torch.nn.functional.gelu(v) * k
+    return torch.nn.functional.elu((S * q).sum(-1, True)), S
+
+
+def _op_tanh_state(q, k, v, S):
+    S = torch.tanh(S + v * k)
+    y = (S * q).sum(-1, True)
+    return y * torch.rsqrt(1 + y * y), S
+
+
+OPERATION_STEPS = [_op_relu_mask, _op_normalise, _op_maximum, _op_silu, _op_sign_clamp, _op_minimum_reciprocal,
+                   _op_mean, _op_softplus_where, _op_gelu_elu, _op_tanh_state]
+
+
+def _operation_case(step, B=2, T=7, H=2, M=8, N=16):
+    import inspect
+    g = torch.Generator().manual_seed(0)
+    n = lambda *s: torch.randn(*s, generator=g)
+    ins = [n(B, T, H, 1, N) * 0.5, n(B, T, H, 1, N) * 0.5, n(B, T, H, M, 1)]
+    if len(inspect.signature(step).parameters) == 5:
+        ins.append(n(B, T, H, 1, N))
+    return ins, [n(B, H, M, N) * 0.5], n(B, T, H, M), n(B, H, M, N)
+
+
+@pytest.mark.parametrize("step", OPERATION_STEPS, ids=lambda f: f.__name__[4:])
+def test_emulated_operations(step):
+    """Activations, masks, clamps and means in the state update and in the
+    output, forward and backward (autograd's formulas for them are imported
+    operation by operation, flex_rnn_b200/graph.py)."""
+    from emu.emu import EmuLauncher
+    ins, sts, dy, dS = _operation_case(step)
+    tu = Tuning(fw_r=2, fw_c=4, fw_mb=8, fw_stage=4, bw_r=2, bw_c=4, seg=2, nslots=2)
+    fwd, bwd, _, _ = build_twopass(step, tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
+    res = fwd(tuple(ins), tuple(sts))
+    dx, ds0 = bwd((dy,), (dS,), tuple(ins), (res[2],), (res[3],))
+    ry, rST, rgx, rgs = O.fwd_bwd(step, ins, sts, [dy], [dS], dtype=torch.float64)
+    for a, b in zip(list(res[:2]) + list(dx) + list(ds0), list(ry) + list(rST) + rgx + rgs):
+        assert a.shape == b.shape and O.rel_err(a, b) < 3e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("step", OPERATION_STEPS, ids=lambda f: f.__name__[4:])
+def test_gpu_operations(step):
+    ins, sts, dy, dS = _operation_case(step, 2, 40, 3, 64, 64)
+    dev = "cuda:0"
+    leaves = [x.to(dev).requires_grad_() for x in ins + sts]
+    f = flex_rnn_b200.jit(step)
+    y, ST = f(*leaves)
+    grads = torch.autograd.grad([y, ST], leaves, [dy.to(dev), dS.to(dev)])
+    torch.cuda.synchronize()
+    assert f.forward_func.kernel_status(dev) == 0
+    ry, rST, rgx, rgs = O.fwd_bwd(step, ins, sts, [dy], [dS], dtype=torch.float64)
+    for a, b in zip([y, ST] + list(grads), list(ry) + list(rST) + rgx + rgs):
+        assert a.shape == b.shape and O.rel_err(a, b) < 3e-5
