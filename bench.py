@@ -47,7 +47,11 @@ WORKLOADS = {
     "rwkv7": ("rwkv7", 8, 1024, 32, 128, 128),
     "mamba2": ("mamba2", 8, 1024, 32, 64, 128),
     "gated_delta_rule": ("gated_delta_rule", 8, 1024, 32, 128, 128),
+    # the scaling configuration: a global batch of 64 sequences of 4096 steps split over the GPUs ("strong" scaling;
+    # 8 sequences per GPU at 8 GPUs, all 64 on one: about 90 GB of checkpoints, row sums and I/O)
+    "gated_delta_rule_c4": ("gated_delta_rule", 64, 4096, 32, 128, 128),
 }
+STRONG = ("gated_delta_rule_c4",)
 # DRAM bytes (read + write) of one backward launch per (batch, head) pair, from the ncu capture summarised in
 # profiles/delta_rule_b2_frnn_fw_bw_ncu_full.md (B=2: 204.0 MB over 64 pairs); traffic grows with the pair count
 NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 204.03e6 / 64, "rwkv7": 782.1e6 / 64}
@@ -245,6 +249,12 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     opname, B, T, H, M, N = WORKLOADS[args.op]
+    strong = args.op in STRONG and not args.batch
+    if strong:
+        assert B % world == 0, "the global batch must divide over the GPUs"
+        B //= world
+    if B * T * H * N * 2 * 3 > 2e9:
+        args.no_e2e = True          # the host-buffer leg would pin several GB per buffer set: kept to the headline sizes
     step_fn = W.STEPS[opname]
     # each rank draws its own shard of the global batch (seed offset by the rank)
     xs_host, dy_host, dS_host = W.synthetic(opname, B, T, H, M, N, torch.bfloat16, seed=rank)
@@ -404,7 +414,7 @@ def main():
         t_hbm = bytes_alg / (hbm * 1e9)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": "fp32", "data": "synthetic",
             "config": {"workload": f"{args.op} fwd+bwd, B{B} T{T} H{H} {M}x{N} per GPU, bf16 I/O, fp32 state and math",
                        "io_dtype": "bf16", "global_batch": B * world, "seq_len": T, "parallelism": f"batch shards x{world}, no collective",
@@ -432,8 +442,9 @@ def main():
         }
         if not args.no_cpu_baseline:
             # one cold pass, then the mean of three (about ten seconds of CPU work on all host threads)
-            cpu_sample(opname, B, T, H, M, N)
-            runs = [cpu_sample(opname, B, T, H, M, N) for _ in range(3)]
+            heads = H if T <= 1024 else 4          # bounds the autograd graph's memory for long sequences
+            cpu_sample(opname, B, T, H, M, N, heads)
+            runs = [cpu_sample(opname, B, T, H, M, N, heads) for _ in range(3)]
             base = runs[-1][0]
             mean_dt = sum(dt for _, dt in runs) / len(runs)
             base["value"] = base["value"] * runs[-1][1] / mean_dt
