@@ -1311,7 +1311,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                   grads: List[GradOut], dy_names: List[str], dnext_names: List[str], tile: Tile,
                   seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
-                  step_unroll: int = 2) -> KernelSource:
+                  step_unroll: int = 2, min_blocks: int = 1) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -1421,7 +1421,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
       f"gradient partials flushed every {kflush} steps")
     kb.emit_tma_issue("bw_issue")
 
-    w(f'extern "C" __global__ void __launch_bounds__({t.NT}, 1)')
+    w(f'extern "C" __global__ void __launch_bounds__({t.NT}, {min_blocks})')
     w.open(f"{kname}({', '.join(kb.param_decl)})")
     w("FRNN_DYN_SMEM(smem);")
     kb.emit_thread_ids()

@@ -93,6 +93,7 @@ class Tuning:
     bw_unroll: int = 4
     slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
     col_major: int = 0       # emit full-tile loops with columns outermost
+    bw_min_blocks: int = 1   # backward CTAs per SM the kernel is built for (2: half the registers and shared memory each)
     pack2: int = 1           # packed fp32x2 arithmetic (two columns per instruction): bit 0 backward, bit 1 forward
     autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
@@ -100,6 +101,12 @@ class Tuning:
 
 
 SMEM_LIMIT = 227 * 1024
+
+
+def _bw_smem_limit(tu) -> int:
+    """Dynamic shared memory a backward CTA may use: all of an SM's, or its share when several CTAs are to be
+    resident (228 KB per SM, 1 KB reserved per CTA)."""
+    return SMEM_LIMIT if tu.bw_min_blocks <= 1 else (228 * 1024) // tu.bw_min_blocks - 1024
 
 
 def default_tuning(B, T, H, M, N, nstates) -> Tuning:
@@ -294,7 +301,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         for kflush, bufs in cands:
             ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
                                tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
-            if ks.smem_bytes <= SMEM_LIMIT:
+            if ks.smem_bytes <= _bw_smem_limit(tu):
                 choice = (sg, kflush, bufs)
                 tu.nslots = nsl
                 break
@@ -380,8 +387,9 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
     for kf, nb in cands:
         bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
                            plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
-                           kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll)
-        if bw.smem_bytes <= SMEM_LIMIT:
+                           kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
+                           min_blocks=max(1, tu.bw_min_blocks))
+        if bw.smem_bytes <= _bw_smem_limit(tu):
             return bw
     return None
 

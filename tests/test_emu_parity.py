@@ -59,6 +59,7 @@ def test_packed_and_scalar_arithmetic(op, pack2):
     ("mamba2", 8, 16, Tuning(fw_r=1, fw_c=8, fw_mb=8, fw_stage=3, bw_r=1, bw_c=4, seg=3, nslots=1)),
     ("rwkv7", 16, 32, Tuning(fw_r=2, fw_c=8, fw_mb=16, fw_stage=8, bw_r=4, bw_c=8, seg=2, nslots=3)),
     ("gated_delta_rule", 16, 16, Tuning(fw_r=4, fw_c=2, fw_mb=16, fw_stage=5, bw_r=2, bw_c=2, seg=1, nslots=2)),
+    ("mamba2", 16, 32, Tuning(fw_r=2, fw_c=8, fw_mb=16, fw_stage=4, bw_r=4, bw_c=4, seg=2, nslots=2, bw_min_blocks=2)),
 ])
 def test_bf16_tilings(op, M, N, tu):
     xs, dy, dS = O.make_case(op, 1, 8, 2, M, N, torch.bfloat16)
