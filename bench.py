@@ -327,15 +327,18 @@ def main():
     value = world * B * T / (ms_per_step * 1e-3)
 
     # end to end through the public API with host buffers (pinned), copies in the timed region
-    pin = [x.detach().cpu().pin_memory() for x in xs_host]
-    pdy, pdS = dy_host.pin_memory(), dS_host.pin_memory()
+    if args.no_e2e:
+        pin, pdy, pdS = [], dy_host, dS_host
+    else:
+        pin = [x.detach().cpu().pin_memory() for x in xs_host]
+        pdy, pdS = dy_host.pin_memory(), dS_host.pin_memory()
     out_host = None
 
     # Three streams, two buffer sets: the host->device copy of step i+1 and the device->host copy of step
     # i-1 run beside the kernels of step i (all of them inside the timed region).
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     host_in = pin + [pdy, pdS]
-    dev_in = [[torch.empty_like(p, device=dev) for p in host_in] for _ in range(2)]
+    dev_in = [[] if args.no_e2e else [torch.empty_like(p, device=dev) for p in host_in] for _ in range(2)]
     dev_out = [None, None]
     ev_in = [torch.cuda.Event() for _ in range(2)]       # inputs of the slot are on the device
     ev_used = [torch.cuda.Event() for _ in range(2)]     # the kernels are done with the slot's inputs
@@ -388,7 +391,7 @@ def main():
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_ms.item())
-    h2d = sum(p.numel() * p.element_size() for p in pin) + pdy.numel() * 2 + pdS.numel() * 2
+    h2d = 0 if args.no_e2e else sum(p.numel() * p.element_size() for p in host_in)
     d2h = sum(h.numel() * h.element_size() for h in out_host) if out_host else 0
 
     if rank == 0:
