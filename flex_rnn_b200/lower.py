@@ -261,10 +261,12 @@ def op_expr(n: Node, a: List[str]) -> str:
 class Body:
     """Emits per-thread code for graph nodes over R x C register tiles."""
 
-    def __init__(self, w: W, tile: Tile, shapes: Dict[str, Shape]):
+    def __init__(self, w: W, tile: Tile, shapes: Dict[str, Shape], pack2: bool = False, col_major: bool = False):
         self.w = w
         self.t = tile
         self.shape = dict(shapes)
+        self.pack2 = pack2            # packed fp32x2 arithmetic for column-varying values
+        self.col_major = col_major    # full-tile loops with the columns outermost
         self.partial: Dict[str, bool] = {}     # value is a per-row-group partial sum
         self.alias: Dict[str, str] = {}        # value name -> name of the register tile that holds it
         self.fused: Dict[str, Node] = {}       # products folded into the packed FMA of their only consumer
@@ -274,10 +276,12 @@ class Body:
     # does the work of two scalar ones, which halves the issue slots the arithmetic needs (the scan
     # kernels are issue-bound, not pipe-bound).  The register arrays stay scalar; a pair is
     # (x[c], x[c+1]) and ptxas allocates it to an aligned register pair.
-    pack2 = False
-
     def can_pack(self) -> bool:
-        return Body.pack2 and self.t.C % 2 == 0
+        return self.pack2 and self.t.C % 2 == 0
+
+    def child(self) -> "Body":
+        """A body for a nested scope: sees this body's values, keeps the same options."""
+        return Body(self.w, self.t, self.shape, self.pack2, self.col_major)
 
     def varies_c(self, a) -> bool:
         return isinstance(a, str) and bool(self.shape[a][1])
@@ -399,11 +403,9 @@ class Body:
         self.shape[name] = s
         self.w(f"float {vname(name)}[{self.size(s)}];")
 
-    col_major = False      # full-tile loops: columns outermost (consecutive FMAs share the row-vector operand)
-
     def loops(self, s: Shape, body):
         w = self.w
-        order = [(1, "c", self.t.C), (0, "r", self.t.R)] if (Body.col_major and s == MN) else \
+        order = [(1, "c", self.t.C), (0, "r", self.t.R)] if (self.col_major and s == MN) else \
                 [(0, "r", self.t.R), (1, "c", self.t.C)]
         opened = 0
         for dim, var, ext in order:
@@ -1116,7 +1118,8 @@ def _stage_inputs(kb: KernelBuilder, p: Problem, used: Sequence[bool], allow_mn:
 
 def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, tile: Tile,
                  dstage: int, dck: int, use_tma: bool, min_blocks: int, prelude: str,
-                 kname: str = "frnn_fw", final_ckpt: bool = False, step_unroll: int = 2) -> KernelSource:
+                 kname: str = "frnn_fw", final_ckpt: bool = False, step_unroll: int = 2, pack2: bool = False,
+                 col_major: bool = False) -> KernelSource:
     """Forward scan.  ``g`` computes [*outputs, *new_states, *aux] from
     [*inputs, *states].  Kernel parameters, in order: used inputs, initial
     states, outputs, final states, checkpoints, aux, error word.  With
@@ -1183,7 +1186,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         w(f"fw_issue(stage, &full[0], 0, min({dstage}, {p.T}), lane, b, h, m0{tma_call});")
         w.close()
 
-    body = Body(w, t, g2.shape)
+    body = Body(w, t, g2.shape, pack2, col_major)
     ckspec = TensorSpec((p.B, p.H, nck_store, p.M, p.N), _contig((p.B, p.H, nck_store, p.M, p.N)), DT_F32)
     for k in range(ns):
         body.declare(p.st_names[k], stcls)
@@ -1224,7 +1227,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     w.open("for (int tl = tl0; tl < tl1; tl++)")
     w("const int t = t0 + tl;")
     w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
-    sub = Body(w, t, body.shape)
+    sub = body.child()
     w.open("")
     for nm in g2.inputs:
         if nm in kb.wk and g2.used_inputs()[g2.inputs.index(nm)]:
@@ -1280,7 +1283,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     return KernelSource(kname, w.text(), (p.M // t.MB, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "tma_items": len(kb.tma_items),
                          "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted],
-                         "tile": [t.R, t.C, t.MB], "packed": Body.pack2},
+                         "tile": [t.R, t.C, t.MB], "packed": bool(pack2)},
                         kb.tmaps)
 
 
@@ -1311,7 +1314,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                   grads: List[GradOut], dy_names: List[str], dnext_names: List[str], tile: Tile,
                   seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
-                  step_unroll: int = 2, min_blocks: int = 1) -> KernelSource:
+                  step_unroll: int = 2, min_blocks: int = 1, pack2: bool = False,
+                  col_major: bool = False) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -1470,7 +1474,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     if not rev:
         ck_fetch(str(first_c), "0")
 
-    body = Body(w, t, g_bw2.shape)
+    body = Body(w, t, g_bw2.shape, pack2, col_major)
     body.shape.update(g_aux2.shape)
     dshape = (p.B, p.H, p.M, p.N)
     for k in range(ns):
@@ -1633,7 +1637,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.open("")
         w(f"const int tl = {tlexpr};")
         w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
-        sub = Body(w, t, body.shape)
+        sub = body.child()
         read_wk_inputs(sub, g_aux2)
         sub.graph(g_aux2)
         for k in range(ns):
@@ -1644,7 +1648,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     def emit_unstep():
         """S_t = S_{t+1} -/+ X_t (reverse mode); expects tl, wkt in scope."""
         w.open("")
-        sub = Body(w, t, body.shape)
+        sub = body.child()
         read_wk_inputs(sub, g_aux2)
         # the update of the state registers is written as one more node, so that the product
         # that forms the increment folds into a packed multiply-add
@@ -1668,7 +1672,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
 
     def emit_bw_step():
         """The backward step proper; expects tl, t, wkt in scope."""
-        sub = Body(w, t, body.shape)
+        sub = body.child()
         read_wk_inputs(sub, g_bw2)
         if alias_next:
             # phase 1 (state registers hold S_{t+1}): every node that does not need S_t
@@ -1876,4 +1880,4 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
                          "reverse": rev, "hoisted": [n.name for n in kb.hoisted], "tile": [t.R, t.C, t.MB],
-                         "packed": Body.pack2}, kb.tmaps)
+                         "packed": bool(pack2)}, kb.tmaps)

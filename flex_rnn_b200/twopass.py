@@ -336,14 +336,14 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Option
     """Emit the forward kernel (for ``tile`` instead of the planned tile, with
     packed arithmetic switched as ``pack`` instead of the tuning's choice, if given)."""
     p, tu = plan.problem, plan.tuning
-    lower.Body.col_major = bool(tu.col_major)
-    lower.Body.pack2 = bool(tu.pack2 & 2) if pack is None else bool(pack)
+    pack2 = bool(tu.pack2 & 2) if pack is None else bool(pack)
     tile = tile or plan.fw_tile
     # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
     stage = tu.fw_stage
     while True:
         fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, tile, stage, plan.D, tu.use_tma,
-                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None, step_unroll=tu.fw_unroll)
+                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None, step_unroll=tu.fw_unroll,
+                          pack2=pack2, col_major=bool(tu.col_major))
         ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
         per_sm = min(max(1, -(-ncta // 148)), 2048 // fw.block, 32)
         if stage <= 4 or fw.smem_bytes * per_sm <= 200 * 1024:
@@ -374,8 +374,6 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
     checkpoint interval and slot count stay what the forward was built for and
     only the flush parameters are re-fitted; None if it does not fit."""
     p, tu = plan.problem, plan.tuning
-    lower.Body.col_major = bool(tu.col_major)
-    lower.Body.pack2 = bool(tu.pack2 & 1)
     sg, kflush, bufs = plan.bw_choice
     cands = [(kflush, bufs)]
     if tile is not None and tile is not plan.bw_tile:
@@ -388,7 +386,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
         bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
                            plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
                            kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
-                           min_blocks=max(1, tu.bw_min_blocks))
+                           min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major))
         if bw.smem_bytes <= _bw_smem_limit(tu):
             return bw
     return None
