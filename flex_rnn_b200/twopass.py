@@ -93,7 +93,8 @@ class Tuning:
     bw_unroll: int = 4
     slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
     col_major: int = 0       # emit full-tile loops with columns outermost
-    bw_min_blocks: int = 1   # backward CTAs per SM the kernel is built for (2: half the registers and shared memory each)
+    bw_min_blocks: int = 0   # backward CTAs per SM the kernel is built for (2: half the registers and shared memory
+                             # each); 0 = two when the planned tile gives CTAs of at most 128 threads, else one
     pack2: int = 1           # packed fp32x2 arithmetic (two columns per instruction): bit 0 backward, bit 1 forward
     autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
@@ -284,6 +285,10 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     choice = None
     import dataclasses
     tu = dataclasses.replace(tu)
+    if tu.bw_min_blocks <= 0:
+        # a (b,h) state small enough for a CTA of four warps leaves room for a second CTA on the SM
+        # (Mamba-2 64x128: 7 % faster backward than one CTA of eight warps)
+        tu.bw_min_blocks = 2 if bw_tile.NT <= 128 and B * H * (M // bw_tile.MB) > 148 else 1
     if reverse is not None:
         pairs = [(sg, tu.nslots) for sg in range(tu.rev_stage, 0, -1)]
     else:
