@@ -111,6 +111,11 @@ def cpu_sample(opname, B, T, H, M, N, heads=None):
     sample (default: all of them, about ten seconds of CPU work)."""
     import torch
     from oracle import naive_oracle as O
+    # all the host threads this process may use (a launcher such as torch.distributed.run pins OMP_NUM_THREADS to 1)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     sb, sh = 1, min(H, heads or H)
     xs, dy, dS = O.make_case(opname, sb, T, sh, M, N, torch.bfloat16)
     t0 = time.perf_counter()
@@ -443,7 +448,7 @@ def main():
             "gpu_launches": 2 * args.steps,
             "clocks": clocks,
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             # one cold pass, then the mean of three (about ten seconds of CPU work on all host threads)
             heads = H if T <= 1024 else 4          # bounds the autograd graph's memory for long sequences
             cpu_sample(opname, B, T, H, M, N, heads)
