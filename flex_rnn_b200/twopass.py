@@ -156,10 +156,11 @@ class Plan:
 
 def _spec(t: th.Tensor) -> TensorSpec:
     ptr_ok = True
-    if t.device.type != "meta":
+    fake = isinstance(t, th._subclasses.fake_tensor.FakeTensor)      # shape propagation only: no address
+    if t.device.type != "meta" and not fake:
         try:
             ptr_ok = t.data_ptr() % 16 == 0
-        except RuntimeError:              # a fake tensor (shape propagation only) has no address
+        except RuntimeError:
             ptr_ok = True
     return TensorSpec(tuple(t.shape), tuple(t.stride()), _DT[t.dtype], ptr_ok)
 

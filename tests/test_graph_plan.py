@@ -169,3 +169,22 @@ def test_sizes_read_inside_the_step_are_the_real_ones():
     y = fwd(ins, sts)[0]
     ry, _, _, _ = O.fwd_bwd(step, list(ins), list(sts), [torch.zeros_like(y)], [torch.zeros_like(sts[0])], dtype=torch.float64)
     assert O.rel_err(y, ry[0]) < 1e-5
+
+
+def test_dry_run_under_fake_tensors():
+    """What a custom op's fake implementation does under torch.compile: plan on
+    fake CUDA tensors (no GPU, no addresses), for an ordinary state and for one
+    that is padded with repeated rows."""
+    import warnings
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from flex_rnn_b200.twopass import build_twopass
+    with FakeTensorMode(), warnings.catch_warnings():
+        warnings.simplefilter("error")
+        bf = dict(device="cuda", dtype=torch.bfloat16)
+        q, v, b = torch.empty(2, 7, 3, 1, 16, **bf), torch.empty(2, 7, 3, 8, 1, **bf), torch.empty(2, 7, 3, 1, 1, **bf)
+        fm, bm = build_twopass(W.delta_rule, (q, q, v, b), (torch.empty(2, 3, 8, 16, **bf),), dryrun=True)
+        assert tuple(fm[0][0]) == (2, 7, 3, 8) and fm[0][2] == torch.bfloat16 and tuple(bm[-1][0]) == (2, 3, 8, 16)
+        i = torch.empty(2, 7, 3, 1, 1, device="cuda")
+        fm, bm = build_twopass(W.mlstm_gates, (i, i), (torch.empty(2, 3, 1, 1, device="cuda"),), dryrun=True)
+        assert [tuple(m[0]) for m in fm[:4]] == [(2, 7, 3, 1)] * 3 + [(2, 3, 1, 1)]
+        assert [tuple(m[0]) for m in bm] == [(2, 7, 3, 1, 1)] * 2 + [(2, 3, 1, 1)]
