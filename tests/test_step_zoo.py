@@ -301,3 +301,28 @@ def test_gpu_operations(step):
     ry, rST, rgx, rgs = O.fwd_bwd(step, ins, sts, [dy], [dS], dtype=torch.float64)
     for a, b in zip([y, ST] + list(grads), list(ry) + list(rST) + rgx + rgs):
         assert a.shape == b.shape and O.rel_err(a, b) < 3e-5
+
+
+@pytest.mark.gpu
+def test_gpu_pipeline_under_torch_compile():
+    """The three-kernel mLSTM pipeline (1x1 gate state padded with repeated
+    rows, one-row normaliser, matrix state) compiled as one graph: the custom
+    ops stay opaque, their fake implementations plan without touching the GPU,
+    and values and gradients equal the eager run."""
+    B, T, H, C = 2, 16, 2, 32
+    g = torch.Generator().manual_seed(4)
+    n = lambda *s: torch.randn(*s, generator=g)
+    dev = "cuda:0"
+    args = [a.to(dev) for a in [n(B, H, T, C), n(B, H, T, C) / C ** .5, n(B, H, T, C), n(B, H, T), n(B, H, T) + 2,
+                                n(B, H, C, C), n(B, H, C), n(B, H, 1)]]
+    ops = [flex_rnn_b200.jit(s) for s in _mlstm_steps()]
+    fn = lambda *a: _mlstm(*ops, *a)
+    compiled = torch.compile(fn, fullgraph=True)
+    out = []
+    for f in (fn, compiled):
+        leaves = [a.clone().requires_grad_() for a in args]
+        res = f(*leaves)
+        grads = torch.autograd.grad([r.sum() for r in res], leaves)
+        out.append(list(res) + list(grads))
+    for a, b in zip(*out):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
