@@ -434,6 +434,9 @@ def main():
                        "bw_kernel": {"grid": list(bw_src.grid), "block": bw_src.block, "smem": bw_src.smem_bytes,
                                      "tile": bw_src.info["tile"][:2], "packed_fp32x2": bw_src.info["packed"]}},
             "fw_ms": fw_avg, "bw_ms": bw_avg,
+            # spread of the per-step device time (forward + backward events of each timed step), rank 0
+            "step_ms_p20_p50_p80": [round(sorted(f + b for f, b in zip(fw_ms, bw_ms))[int(q * (len(fw_ms) - 1))], 4)
+                                    for q in (0.2, 0.5, 0.8)],
             "roofline_fraction_step": max(t_fp32, t_hbm) / (ms_per_step * 1e-3),
             "roofline": {"bound": "fp32", "kernel": bw_src.name, "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp32_peak,
