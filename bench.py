@@ -54,7 +54,8 @@ WORKLOADS = {
 STRONG = ("gated_delta_rule_c4",)
 # DRAM bytes (read + write) of one backward launch per (batch, head) pair, from the ncu capture summarised in
 # profiles/*_b2_frnn_fw_bw_ncu_full.md (B=2, 64 pairs; Delta Rule 204.0 MB); traffic grows with the pair count
-NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 204.03e6 / 64, "rwkv7": 782.1e6 / 64, "mamba2": 355.5e6 / 64}
+NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 204.03e6 / 64, "rwkv7": 782.1e6 / 64, "mamba2": 355.5e6 / 64,
+                            "gated_delta_rule": 690.5e6 / 64}
 METRIC = "fwd+bwd tokens/s"
 UNIT = "tokens/s"
 
