@@ -338,18 +338,20 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     return plan, fw_meta, bw_meta
 
 
-def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Optional[bool] = None) -> lower.KernelSource:
-    """Emit the forward kernel (for ``tile`` instead of the planned tile, with
-    packed arithmetic switched as ``pack`` instead of the tuning's choice, if given)."""
+def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Optional[bool] = None,
+                     stage: Optional[int] = None, unroll: Optional[int] = None) -> lower.KernelSource:
+    """Emit the forward kernel.  The optional arguments replace the plan's
+    choices: the tile, packed arithmetic on or off, timesteps staged per chunk
+    and the unroll factor of the step loop."""
     p, tu = plan.problem, plan.tuning
     pack2 = bool(tu.pack2 & 2) if pack is None else bool(pack)
     tile = tile or plan.fw_tile
     # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
-    stage = tu.fw_stage
+    stage = max(1, min(stage or tu.fw_stage, p.T))
     while True:
         fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, tile, stage, plan.D, tu.use_tma,
-                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None, step_unroll=tu.fw_unroll,
-                          pack2=pack2, col_major=bool(tu.col_major))
+                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None,
+                          step_unroll=unroll or tu.fw_unroll, pack2=pack2, col_major=bool(tu.col_major))
         ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
         per_sm = min(max(1, -(-ncta // 148)), 2048 // fw.block, 32)
         if stage <= 4 or fw.smem_bytes * per_sm <= 200 * 1024:
@@ -654,11 +656,15 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         tuned["fw"] = True
         best = None
         default_pack = bool(plan.tuning.pack2 & 2)
-        cands = [(tile, default_pack) for tile in forward_tile_candidates(plan)] + [(plan.fw_tile, not default_pack)]
-        for tile, pack in cands:
+        cands = [(tile, default_pack, None) for tile in forward_tile_candidates(plan)]
+        cands.append((plan.fw_tile, not default_pack, None))
+        if plan.reverse is None and plan.D <= 16:
+            # one chunk per checkpoint interval, step loop fully unrolled (Gated Delta: 9 % faster forward)
+            cands.append((plan.fw_tile, default_pack, plan.D))
+        for tile, pack, chunk in cands:
             try:
-                planned = tile is plan.fw_tile and pack == default_pack
-                ks = fw_src if planned else generate_forward(plan, tile, pack)
+                planned = tile is plan.fw_tile and pack == default_pack and chunk is None
+                ks = fw_src if planned else generate_forward(plan, tile, pack, stage=chunk, unroll=chunk)
                 launcher = launch_fw if planned else make(ks)
                 launcher(ptrs, device)                                   # compile + warm up
                 ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
