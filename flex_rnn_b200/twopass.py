@@ -286,7 +286,8 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     choice = None
     import dataclasses
     tu = dataclasses.replace(tu)
-    if tu.bw_min_blocks <= 0:
+    auto_blocks = tu.bw_min_blocks <= 0
+    if auto_blocks:
         # a (b,h) state small enough for a CTA of four warps leaves room for a second CTA on the SM
         # (Mamba-2 64x128: 7 % faster backward than one CTA of eight warps)
         tu.bw_min_blocks = 2 if bw_tile.NT <= 128 and B * H * (M // bw_tile.MB) > 148 else 1
@@ -297,22 +298,27 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         pairs = ([(2, 4)] if tu.slot_search and T >= 8 else []) + [(sg, tu.nslots) for sg in range(tu.seg, 0, -1)]
         if tu.nslots > 1:
             pairs += [(sg, 1) for sg in range(tu.seg, 0, -1)]
-    ks = None
-    for sg, nsl in pairs:
-        k = max(1, tu.kflush)
-        cands = []
-        while k >= 1:
-            cands += [(k, 2), (k, 1)]
-            k //= 2
-        for kflush, bufs in cands:
-            ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
-                               tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
-            if ks.smem_bytes <= _bw_smem_limit(tu):
-                choice = (sg, kflush, bufs)
-                tu.nslots = nsl
+    while choice is None:
+        ks = None
+        for sg, nsl in pairs:
+            k = max(1, tu.kflush)
+            cands = []
+            while k >= 1:
+                cands += [(k, 2), (k, 1)]
+                k //= 2
+            for kflush, bufs in cands:
+                ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
+                                   tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
+                if ks.smem_bytes <= _bw_smem_limit(tu):
+                    choice = (sg, kflush, bufs)
+                    tu.nslots = nsl
+                    break
+            if choice or ks is None:
                 break
-        if choice or ks is None:
-            break
+        if choice is None and auto_blocks and tu.bw_min_blocks > 1:
+            tu.bw_min_blocks = 1          # half an SM's shared memory is not enough: one CTA per SM after all
+            continue
+        break
     seg0 = pairs[0][0]
     if choice is None:
         raise lower.LoweringError(f"the backward kernel of a {M}x{N} state does not fit shared memory")
