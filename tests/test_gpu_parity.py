@@ -181,3 +181,25 @@ def test_check_grad_and_torch_compile():
     g2 = torch.autograd.grad([y2.sum(), S2.sum()], leaves2)
     for a, b in zip(g, g2):
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op_name", ["delta_rule", "mamba2"])
+def test_more_ctas_than_sms_small_state(op_name):
+    """With more (b,h) pairs than SMs and a state small enough for a CTA of four
+    warps the backward is built for two CTAs per SM (half the shared memory
+    each); reverse re-step and recomputing mode.  Checked on a few (b,h) slices."""
+    B, T, H, M, N = 5, 24, 32, 64, 64
+    xs, dy, dS = O.make_case(op_name, B, T, H, M, N, torch.float32)
+    y, ST, grads, op = run_gpu(op_name, xs, dy, dS)
+    assert op.forward_func.plan.tuning.bw_min_blocks == 2
+    for b, h in ((0, 0), (2, 17), (4, 31)):
+        sl = [x[b:b + 1, :, h:h + 1] if x.shape[0] > 1 else x[:, :, h:h + 1] for x in xs[:-1]]
+        ry, rST, rgx, rgs = O.fwd_bwd(O.STEPS[op_name], sl, [xs[-1][b:b + 1, h:h + 1]], [dy[b:b + 1, :, h:h + 1]],
+                                      [dS[b:b + 1, h:h + 1]], dtype=torch.float64)
+        assert O.rel_err(y[b:b + 1, :, h:h + 1], ry[0]) < 1e-5 and O.rel_err(ST[b:b + 1, h:h + 1], rST[0]) < 1e-5
+        for g, r, x in zip(grads, rgx + rgs, xs):
+            if x.dim() == 5 and x.shape[0] == 1:
+                continue                        # summed over the batch: not a per-slice quantity
+            gs = g[b:b + 1, :, h:h + 1] if x.dim() == 5 else g[b:b + 1, h:h + 1]
+            assert O.rel_err(gs, r) < 1e-5, (op_name, b, h)
