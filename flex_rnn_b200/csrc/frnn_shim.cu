@@ -8,6 +8,7 @@
 #include <dlfcn.h>
 #include <nvrtc.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -43,6 +44,7 @@ struct Nvrtc {
     nvrtcResult (*GetCUBIN)(nvrtcProgram, char*);
     nvrtcResult (*DestroyProgram)(nvrtcProgram*);
     const char* (*GetErrorString)(nvrtcResult);
+    nvrtcResult (*Version)(int*, int*);
     std::string why;
 };
 
@@ -75,6 +77,7 @@ Nvrtc* nvrtc() {
         *(void**)&n.GetCUBIN = sym("nvrtcGetCUBIN");
         *(void**)&n.DestroyProgram = sym("nvrtcDestroyProgram");
         *(void**)&n.GetErrorString = sym("nvrtcGetErrorString");
+        *(void**)&n.Version = sym("nvrtcVersion");
         if (!ok) { dlclose(n.lib); n.lib = nullptr; }
     });
     return n.lib ? &n : nullptr;
@@ -142,7 +145,16 @@ struct frnn_module {
 
 extern "C" {
 
-int frnn_abi_version(void) { return 1; }
+int frnn_abi_version(void) { return 2; }
+
+int frnn_nvrtc_version(int* major, int* minor) {
+    if (!major || !minor) return fail(FRNN_E_ARG, "frnn_nvrtc_version: bad argument");
+    Nvrtc* n = nvrtc();
+    if (!n) return fail(FRNN_E_NVRTC, "NVRTC is not available (libnvrtc.so.12 could not be loaded)");
+    nvrtcResult r = n->Version(major, minor);
+    if (r != NVRTC_SUCCESS) return fail(FRNN_E_NVRTC, "nvrtcVersion: %s", n->GetErrorString(r));
+    return FRNN_OK;
+}
 
 const char* frnn_last_error(void) { return g_err.c_str(); }
 
@@ -292,6 +304,51 @@ int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, 
 
 }  // extern "C"
 
+// ---- kernel error word ---------------------------------------------------------
+
+namespace {
+const char* kernel_code_text(int code) {
+    switch (code) {
+        case 1: return "a staged-input copy did not arrive within the wait limit";
+        case 2: return "a checkpoint copy did not arrive within the wait limit";
+        default: return "unknown code";
+    }
+}
+}  // namespace
+
+extern "C" {
+
+int frnn_status_post(int* err_word_dev, int* host_word, void* stream) {
+    if (!err_word_dev || !host_word) return fail(FRNN_E_ARG, "frnn_status_post: bad argument");
+    cudaError_t e = cudaMemcpyAsync(host_word, err_word_dev, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FRNN_E_DRIVER, "frnn_status_post: %s", cudaGetErrorString(e));
+    return FRNN_OK;
+}
+
+int frnn_status_check(int* host_word, int* err_word_dev, void* stream) {
+    if (!host_word) return fail(FRNN_E_ARG, "frnn_status_check: bad argument");
+    const int code = *(volatile int*)host_word;
+    if (!code) return FRNN_OK;
+    *(volatile int*)host_word = 0;
+    if (err_word_dev) cudaMemsetAsync(err_word_dev, 0, sizeof(int), (cudaStream_t)stream);   // the word is sticky: clear it
+    return fail(FRNN_E_KERNEL, "a kernel reported error %d through its error word (%s); its outputs are not valid",
+                code, kernel_code_text(code));
+}
+
+int frnn_status(int* err_word_dev, void* stream) {
+    if (!err_word_dev) return fail(FRNN_E_ARG, "frnn_status: bad argument");
+    int code = 0;
+    cudaError_t e = cudaMemcpyAsync(&code, err_word_dev, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(FRNN_E_DRIVER, "frnn_status: %s", cudaGetErrorString(e));
+    if (!code) return FRNN_OK;
+    cudaMemsetAsync(err_word_dev, 0, sizeof(int), (cudaStream_t)stream);
+    return fail(FRNN_E_KERNEL, "a kernel reported error %d through its error word (%s); its outputs are not valid",
+                code, kernel_code_text(code));
+}
+
+}  // extern "C"
+
 // ---- launch with the kernel's scratch buffers in library-owned static memory ----
 
 #define FRNN_STATIC_SCRATCH_BYTES (32u << 20)
@@ -312,22 +369,36 @@ int frnn_launch_static_scratch(frnn_module_t m, int kernel, const unsigned grid[
                                unsigned smem_bytes, void* stream, void* const* args, int nargs,
                                const int* scratch_arg, const size_t* scratch_bytes, int nscratch) {
     enum { MAX_ARGS = 64 };
-    if (!m || !args || nargs <= 0 || nargs > MAX_ARGS || nscratch <= 0 || !scratch_arg || !scratch_bytes)
-        return fail(FRNN_E_ARG, "frnn_launch_static_scratch: bad argument (at most %d kernel parameters)", (int)MAX_ARGS);
+    if (!m || !args || nargs <= 0 || nargs > MAX_ARGS || nscratch <= 0 || nscratch > nargs || !scratch_arg || !scratch_bytes)
+        return fail(FRNN_E_ARG,
+                    "frnn_launch_static_scratch: bad argument (at most %d kernel parameters, and no more scratch "
+                    "parameters than kernel parameters)", (int)MAX_ARGS);
+    // everything that can be refused is refused before the array is looked up or anything is launched
     // carve 256-byte aligned slices out of the static array; refuse what does not fit
     size_t off[MAX_ARGS];
+    bool taken[MAX_ARGS] = {false};
     size_t total = 0;
     for (int i = 0; i < nscratch; i++) {
         if (scratch_arg[i] < 0 || scratch_arg[i] >= nargs)
             return fail(FRNN_E_ARG, "frnn_launch_static_scratch: scratch parameter index %d out of range", scratch_arg[i]);
+        if (taken[scratch_arg[i]])
+            return fail(FRNN_E_ARG, "frnn_launch_static_scratch: scratch parameter index %d is listed twice", scratch_arg[i]);
+        taken[scratch_arg[i]] = true;
         off[i] = total;
-        total += (scratch_bytes[i] + 255) / 256 * 256;
-        if (total > (size_t)FRNN_STATIC_SCRATCH_BYTES || scratch_bytes[i] > (size_t)FRNN_STATIC_SCRATCH_BYTES)
+        if (scratch_bytes[i] > (size_t)FRNN_STATIC_SCRATCH_BYTES)
+            total = (size_t)FRNN_STATIC_SCRATCH_BYTES + 1;
+        else
+            total += (scratch_bytes[i] + 255) / 256 * 256;
+        if (total > (size_t)FRNN_STATIC_SCRATCH_BYTES)
             return fail(FRNN_E_ARG,
                         "frnn_launch_static_scratch: the kernel needs more scratch than the library's static "
                         "buffer holds (capacity %zu bytes); use frnn_launch with caller-allocated scratch",
                         (size_t)FRNN_STATIC_SCRATCH_BYTES);
     }
+    if (kernel < 0 || kernel >= (int)m->fn.size() || !grid || !block)
+        return fail(FRNN_E_ARG, "frnn_launch_static_scratch: bad kernel index, grid or block");
+    if (!grid[0] || !grid[1] || !grid[2] || !block[0] || block[0] * block[1] * block[2] > 1024)
+        return fail(FRNN_E_ARG, "frnn_launch_static_scratch: empty grid or oversized block");
     // one-time set-up per device: the host-side name of a __device__ array is not a device
     // address; ask the runtime for the address in the current device's context
     int dev = -1;
@@ -393,7 +464,7 @@ extern "C" {
 
 int frnn_l2_flush(void* buf, size_t bytes, void* stream) {
     if (!buf || bytes < 16) return fail(FRNN_E_ARG, "frnn_l2_flush: bad argument");
-    static unsigned pattern = 0;
+    static std::atomic<unsigned> pattern{0};
     frnn_flush_kernel<<<1184, 256, 0, (cudaStream_t)stream>>>((uint4*)buf, bytes / 16, ++pattern);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(FRNN_E_LAUNCH, "frnn_l2_flush: %s", cudaGetErrorString(e));

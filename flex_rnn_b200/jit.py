@@ -112,29 +112,31 @@ class jit:
             fw_meta, _ = self._dry_metas(inputs, state)
             return materialise(fw_meta, args[0].device)
 
+        # The backward op also receives the initial states.  Their values are never read (the kernels
+        # restart from checkpoint 0); they identify the specialisation exactly: two calls with the same
+        # inputs but states of other strides or dtype are different kernels.
         @th.library.custom_op(f"flex_rnn_b200::bw_{uid}", mutates_args=(),
-                              schema=schema(nout + 2 * nst + nin + _N_PACKED_AUX, nin + nst))
+                              schema=schema(nout + 3 * nst + nin + _N_PACKED_AUX, nin + nst))
         def bw_op(*args):
-            dout, dstT, inputs, store, aux = split_list(args, [nout, nst, nin, nst, _N_PACKED_AUX])
-            # the state values are not saved; only their metadata matters for the cache key
-            key_state = tuple(th.empty_strided(d.shape, d.stride(), dtype=d.dtype, device="meta") for d in dstT)
-            _, backward, _, bw_meta = self._lookup_for_backward(inputs, store)
+            dout, dstT, inputs, state0, store, aux = split_list(args, [nout, nst, nin, nst, nst, _N_PACKED_AUX])
+            _, backward, _, bw_meta = self._lookup_for_backward(inputs, state0)
             dx, ds0 = backward(dout, dstT, inputs, store, aux)
             verify_meta(dx + ds0, materialise(bw_meta, "meta"))
             return (*dx, *ds0)
 
         @bw_op.register_fake
         def _(*args):
-            dout, dstT, inputs, store, aux = split_list(args, [nout, nst, nin, nst, _N_PACKED_AUX])
-            _, bw_meta = self._lookup_for_backward(inputs, store, dry=True)
+            dout, dstT, inputs, state0, store, aux = split_list(args, [nout, nst, nin, nst, nst, _N_PACKED_AUX])
+            _, bw_meta = self._lookup_for_backward(inputs, state0, dry=True)
             return materialise(bw_meta, args[0].device)
 
         def setup_context(ctx, inputs, output):
             ctx.set_materialize_grads(False)
-            ctx.save_for_backward(*inputs[:nin], *output[nout + nst:])
+            ctx.save_for_backward(*inputs, *output[nout + nst:])
             ctx.out_meta = tuple(o.to("meta") for o in output[:nout + nst])
 
         def backward(ctx, *grads):
+            # upstream gradients that autograd leaves out are zeros (reference: flex_rnn/jit.py:76-80)
             grads = list(grads[:nout + nst])
             dev = ctx.saved_tensors[0].device
             for i, m in enumerate(ctx.out_meta):
@@ -146,17 +148,16 @@ class jit:
         self._fw_op, self._bw_op = fw_op, bw_op
         return lambda *args: fw_op(*args)[:nout + nst]
 
-    def _lookup_for_backward(self, inputs, store, dry=False):
-        """Find the specialisation whose inputs match (the backward op does not
-        receive the initial states)."""
-        sig_in = _signature(tuple(inputs))[:-1]
+    def _lookup_for_backward(self, inputs, state0, dry=False):
+        """The specialisation a forward call made for exactly these inputs and
+        initial states (shapes, strides, dtypes, device)."""
+        key = _signature(tuple(inputs) + tuple(state0))
         table = self._metas if dry else self._compiled
-        for key, val in table.items():
-            if key[:len(inputs)] == sig_in:
-                if dry:
-                    return val
-                return val
-        raise AssertionError("backward called for inputs that no forward call has specialised")
+        if key not in table:
+            if dry:
+                return self._dry_metas(inputs, state0)
+            raise AssertionError("backward called for arguments that no forward call has specialised")
+        return table[key]
 
 
 def simplified_naive(step, *args):

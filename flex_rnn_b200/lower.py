@@ -726,7 +726,11 @@ class KernelBuilder:
         if const_off:
             base = f"{const_off}L + " + base
         item = StagedItem(key, cls, spec.dt, ptr, length, base, st_t, inner, tma, 0, rowb)
-        if tma and self.tensor_tma and length <= 256 and self.D <= 256 and (const_off * e) % 16 == 0:
+        # a dim of extent > 1 with stride 0 (an input expanded over B, T or H) has no tensor-map form:
+        # such inputs take the per-timestep bulk copies, which index with the given strides
+        expanded = any(spec.shape[dims[d]] > 1 and spec.stride[dims[d]] == 0 for d in ("b", "t", "h", "v"))
+        if (tma and self.tensor_tma and not expanded and length <= 256 and self.D <= 256
+                and (const_off * e) % 16 == 0):
             # one 4-D box (vector, head, D timesteps, batch) per chunk instead of one bulk copy per timestep
             ext = lambda d: spec.shape[d] if spec.shape[d] > 1 else 1
             pad = max(16, (ext(dims["v"]) * e + 15) // 16 * 16)

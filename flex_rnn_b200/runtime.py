@@ -19,7 +19,8 @@ LIB_PATH = os.path.join(HERE, "libfrnn_b200.so")
 
 SYMBOLS = ["frnn_abi_version", "frnn_last_error", "frnn_compile", "frnn_free", "frnn_module_load",
            "frnn_module_unload", "frnn_launch", "frnn_kernel_attrs", "frnn_l2_flush", "frnn_fp32_peak_probe",
-           "frnn_launch_static_scratch", "frnn_static_scratch_capacity", "frnn_tensor_map_encode"]
+           "frnn_launch_static_scratch", "frnn_static_scratch_capacity", "frnn_tensor_map_encode",
+           "frnn_nvrtc_version", "frnn_status", "frnn_status_post", "frnn_status_check"]
 
 
 class FrnnError(RuntimeError):
@@ -57,6 +58,10 @@ def lib() -> ctypes.CDLL:
         L.frnn_static_scratch_capacity.restype = sz
         L.frnn_tensor_map_encode.argtypes = [vp, vp, cu, cu, ctypes.POINTER(ctypes.c_uint64),
                                              ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint32)]
+        L.frnn_nvrtc_version.argtypes = [ctypes.POINTER(ci), ctypes.POINTER(ci)]
+        L.frnn_status.argtypes = [vp, vp]
+        L.frnn_status_post.argtypes = [vp, vp, vp]
+        L.frnn_status_check.argtypes = [vp, vp, vp]
         L.frnn_l2_flush.argtypes = [vp, sz, vp]
         L.frnn_fp32_peak_probe.argtypes = [vp, ci, vp, ctypes.POINTER(ctypes.c_double)]
         _lib = L
@@ -69,13 +74,32 @@ def _check(rc: int, what: str):
 
 
 _cubin_cache: Dict[str, Tuple[bytes, str]] = {}
+_toolchain_tag: Optional[str] = None
+
+
+def toolchain_tag() -> str:
+    """What a cached cubin depends on besides its source: the NVRTC that
+    compiled it and the ABI of the library whose prelude it was generated for."""
+    global _toolchain_tag
+    if _toolchain_tag is None:
+        L = lib()
+        major, minor = ctypes.c_int(), ctypes.c_int()
+        _check(L.frnn_nvrtc_version(ctypes.byref(major), ctypes.byref(minor)), "frnn_nvrtc_version")
+        _toolchain_tag = f"nvrtc{major.value}.{minor.value}-abi{L.frnn_abi_version()}-sm_100a"
+    return _toolchain_tag
+
+
+def cache_key(src: str, opts: Sequence[str] = ()) -> str:
+    return hashlib.sha256("\0".join([toolchain_tag(), src, *opts]).encode()).hexdigest()
 
 
 def compile_cubin(src: str, opts: Sequence[str] = ()) -> Tuple[bytes, str]:
     """NVRTC-compile ``src`` for sm_100a.  Returns (cubin, compiler log).
-    Needs no GPU.  Results are cached by source hash in memory and, when
-    ``FRNN_CACHE_DIR`` is set, on disk."""
-    key = hashlib.sha256((src + "\0" + "\0".join(opts)).encode()).hexdigest()
+    Needs no GPU.  Results are cached in memory and, when ``FRNN_CACHE_DIR`` is
+    set, on disk, keyed by the source, the options, the NVRTC version and the
+    library's ABI version (the reference keys on the source hash alone,
+    flex_rnn/to_cuda.py:264).  A cached entry's log reads "(cached)"."""
+    key = cache_key(src, opts)
     if key in _cubin_cache:
         return _cubin_cache[key]
     cdir = os.environ.get("FRNN_CACHE_DIR")
@@ -99,8 +123,10 @@ def compile_cubin(src: str, opts: Sequence[str] = ()) -> Tuple[bytes, str]:
     L.frnn_free(cub)
     if cdir:
         os.makedirs(cdir, exist_ok=True)
-        with open(os.path.join(cdir, key + ".cubin"), "wb") as f:
+        tmp = os.path.join(cdir, f"{key}.{os.getpid()}.tmp")
+        with open(tmp, "wb") as f:
             f.write(data)
+        os.replace(tmp, os.path.join(cdir, key + ".cubin"))     # atomic: several ranks may fill one cache
     _cubin_cache[key] = (data, logtxt)
     return data, logtxt
 
@@ -183,6 +209,21 @@ class Module:
         if getattr(self, "_h", None):
             lib().frnn_module_unload(self._h)
             self._h = None
+
+
+def status(err_word_ptr: int, stream: int):
+    """Synchronous check of a kernel error word; raises FrnnError if a kernel reported a timed-out wait."""
+    _check(lib().frnn_status(ctypes.c_void_p(err_word_ptr), ctypes.c_void_p(stream)), "kernel status")
+
+
+def status_post(err_word_ptr: int, host_word_ptr: int, stream: int):
+    _check(lib().frnn_status_post(ctypes.c_void_p(err_word_ptr), ctypes.c_void_p(host_word_ptr), ctypes.c_void_p(stream)),
+           "frnn_status_post")
+
+
+def status_check(host_word_ptr: int, err_word_ptr: int, stream: int):
+    _check(lib().frnn_status_check(ctypes.c_void_p(host_word_ptr), ctypes.c_void_p(err_word_ptr), ctypes.c_void_p(stream)),
+           "kernel status")
 
 
 def l2_flush(buf_ptr: int, nbytes: int, stream: int):

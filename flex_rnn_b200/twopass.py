@@ -98,10 +98,52 @@ class Tuning:
     pack2: int = 1           # packed fp32x2 arithmetic (two columns per instruction): bit 0 backward, bit 1 forward
     autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
+    fw_variant: int = -1     # >= 0: use this member of forward_variants(plan) untimed (tests, reproducible runs)
+    bw_variant: int = -1     # >= 0: use this member of backward_variants(plan) untimed
     use_tma: bool = True
 
 
 SMEM_LIMIT = 227 * 1024
+B200_SMS = 148      # used only when planning without a device (meta tensors, dry runs); else read from the device
+
+
+def sm_count(device) -> int:
+    """Streaming multiprocessors of ``device`` (a CUDA device), else a B200's."""
+    if getattr(device, "type", None) == "cuda" and th.cuda.is_available():
+        return th.cuda.get_device_properties(device).multi_processor_count
+    return B200_SMS
+
+
+class _DeviceStatus:
+    """The error word the kernels of one device report through, and a pinned
+    host mirror of it.  After every launch the word is copied to the mirror
+    behind the kernel on the same stream (no wait); the next call looks at the
+    mirror first and raises if a kernel of an earlier call gave up on a wait,
+    which costs the hot path no synchronisation."""
+
+    def __init__(self, device):
+        self.word = th.zeros(1, dtype=th.int32, device=device)
+        self.host = th.zeros(1, dtype=th.int32).pin_memory()
+
+    def check(self, stream: int):
+        from . import runtime
+        runtime.status_check(self.host.data_ptr(), self.word.data_ptr(), stream)
+
+    def post(self, stream: int):
+        from . import runtime
+        runtime.status_post(self.word.data_ptr(), self.host.data_ptr(), stream)
+
+
+_status: Dict[int, _DeviceStatus] = {}
+
+
+def device_status(device) -> _DeviceStatus:
+    """Status words of a CUDA device (created on first use)."""
+    device = th.device(device)
+    idx = device.index if device.index is not None else th.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = _DeviceStatus(th.device("cuda", idx))
+    return _status[idx]
 
 
 def _bw_smem_limit(tu) -> int:
@@ -232,6 +274,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             raise AssertionError("Only torch.sum(x, dim=-1, keepdim=True) is supported")
 
     tu = tuning or default_tuning(B, T, H, M, N, nst)
+    n_sm = sm_count(inputs[0].device if inputs else state[0].device)
     # register budget: every state (and, in the backward, its gradient) and every matrix-per-head input
     # (and its gradient) is an R x C tile per thread
     n_mat = sum(1 for c in in_cls if c == MN)
@@ -290,7 +333,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     if auto_blocks:
         # a (b,h) state small enough for a CTA of four warps leaves room for a second CTA on the SM
         # (Mamba-2 64x128: 7 % faster backward than one CTA of eight warps)
-        tu.bw_min_blocks = 2 if bw_tile.NT <= 128 and B * H * (M // bw_tile.MB) > 148 else 1
+        tu.bw_min_blocks = 2 if bw_tile.NT <= 128 and B * H * (M // bw_tile.MB) > n_sm else 1
     if reverse is not None:
         pairs = [(sg, tu.nslots) for sg in range(tu.rev_stage, 0, -1)]
     else:
@@ -341,6 +384,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     plan = Plan(prob, joint, g_fw, g_re, g_bw, aux, nout, nst, grads, tu, fw_tile, bw_tile, D, nck,
                 g_fw0.count_mn_ops(), joint.pruned(jout, "all").count_mn_ops(), reverse, choice)
     plan.dy_names, plan.dnext_names = dy_names, dnext_names   # type: ignore[attr-defined]
+    plan.n_sm = n_sm                                            # type: ignore[attr-defined]
     return plan, fw_meta, bw_meta
 
 
@@ -359,7 +403,7 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Option
                           tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None,
                           step_unroll=unroll or tu.fw_unroll, pack2=pack2, col_major=bool(tu.col_major))
         ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
-        per_sm = min(max(1, -(-ncta // 148)), 2048 // fw.block, 32)
+        per_sm = min(max(1, -(-ncta // getattr(plan, "n_sm", B200_SMS))), 2048 // fw.block, 32)
         if stage <= 4 or fw.smem_bytes * per_sm <= 200 * 1024:
             break
         stage //= 2
@@ -381,6 +425,24 @@ def forward_tile_candidates(plan: Plan) -> List[lower.Tile]:
             seen.add((t.R, t.C, t.MB))
             out.append(t)
     return out
+
+
+def forward_variants(plan: Plan) -> List[dict]:
+    """Keyword arguments of ``generate_forward`` for every forward kernel the
+    autotuner may pick; member 0 is the planned kernel."""
+    default_pack = bool(plan.tuning.pack2 & 2)
+    out = [dict(tile=t, pack=default_pack, stage=None, unroll=None) for t in forward_tile_candidates(plan)]
+    out.append(dict(tile=plan.fw_tile, pack=not default_pack, stage=None, unroll=None))
+    if plan.reverse is None and plan.D <= 16:
+        # one chunk per checkpoint interval, step loop fully unrolled
+        out.append(dict(tile=plan.fw_tile, pack=default_pack, stage=plan.D, unroll=plan.D))
+    return out
+
+
+def backward_variants(plan: Plan) -> List[dict]:
+    """Keyword arguments of ``generate_backward`` for every backward kernel the
+    autotuner may pick; member 0 is the planned kernel."""
+    return [dict(tile=t) for t in backward_tile_candidates(plan)]
 
 
 def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional[lower.KernelSource]:
@@ -557,7 +619,7 @@ def _build_row_padded(step, inputs, state, Mp, dryrun, tuning, _launcher):
                     for m, dp in zip(stT_meta, ds0_p))
         return dxs, ds0
 
-    for name in ("plan", "sources", "launchers", "kernel_status"):
+    for name in ("plan", "sources", "launchers", "kernel_status", "tuned"):
         setattr(forward, name, getattr(fwd_p, name))
     forward.padded_rows = Mp                # type: ignore[attr-defined]
     return forward, backward, fw_meta, bw_meta
@@ -585,6 +647,14 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         raise RuntimeError("flex_rnn_b200 runs on CUDA devices only (there is no CPU path); "
                            "use the .naive method for a CPU evaluation of the step function")
     fw_src, bw_src = generate(plan)
+    tu0 = plan.tuning
+    forced_fw, forced_bw = tu0.fw_variant >= 0, tu0.bw_variant >= 0
+    if forced_fw and tu0.fw_variant > 0:
+        fw_src = generate_forward(plan, **forward_variants(plan)[tu0.fw_variant])
+    if forced_bw and tu0.bw_variant > 0:
+        bw_src = generate_backward(plan, **backward_variants(plan)[tu0.bw_variant])
+        if bw_src is None:
+            raise lower.LoweringError("the requested backward variant does not fit shared memory")
     p = plan.problem
     nin, nst, nout = len(inputs), plan.n_st, plan.n_out
     make = _launcher or _CudaLauncher
@@ -596,24 +666,35 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
     st_align = [x.data_ptr() % 16 == 0 for x in state]
     fw_used = plan.g_fw.used_inputs()
     bw_used = [a or b for a, b in zip(plan.g_re.used_inputs(), plan.g_bw.used_inputs())]
-    err_words: Dict[int, th.Tensor] = {}
+    emulated = _launcher is not None
+    emu_words: Dict[str, th.Tensor] = {}
 
     def err_word(device):
-        idx = device.index
-        if idx not in err_words:
-            err_words[idx] = th.zeros(1, dtype=th.int32, device=device)
-        return err_words[idx]
+        if emulated:          # the test seam runs on host tensors
+            if "w" not in emu_words:
+                emu_words["w"] = th.zeros(1, dtype=th.int32, device=device)
+            return emu_words["w"]
+        return device_status(device).word
 
     strict = os.environ.get("FRNN_CHECK", "0") not in ("", "0")
 
+    def check_before(device):
+        """Raise if a kernel launched by an earlier call on this device reported
+        a timed-out wait (its outputs were not valid).  No synchronisation."""
+        if not emulated:
+            device_status(device).check(th.cuda.current_stream(device).cuda_stream)
+
     def check_status(device, what):
-        """With FRNN_CHECK=1: synchronise after every launch and raise if a
-        kernel reported a timed-out wait (off by default: it serialises)."""
-        if strict and device.type == "cuda":
-            code = int(err_word(device).item())
-            if code:
-                raise RuntimeError(f"flex_rnn_b200 {what} kernel reported error {code} "
-                                   "(1: staged inputs, 2: checkpoint copy did not arrive in time)")
+        """After a launch: queue the copy of the error word to its host mirror
+        (read by the next call).  With FRNN_CHECK=1 also wait and raise now."""
+        if emulated:
+            return
+        from . import runtime
+        stream = th.cuda.current_stream(device).cuda_stream
+        if strict:
+            runtime.status(device_status(device).word.data_ptr(), stream)
+        else:
+            device_status(device).post(stream)
 
     def check_align(ts, flags, what):
         for i, (t, f) in enumerate(zip(ts, flags)):
@@ -623,71 +704,67 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
     # timing alternative tilings costs a few NVRTC compilations: only worth it for work of benchmark size
     no_tune = (_launcher is not None or not plan.tuning.autotune
                or p.B * p.T * p.H * p.M * p.N < plan.tuning.autotune_min_work)
-    tuned = {"fw": no_tune, "launch_fw": launch_fw, "fw_src": fw_src, "bw": no_tune, "launch_bw": launch_bw,
-             "bw_src": bw_src}
+    tuned = {"fw": no_tune or forced_fw, "launch_fw": launch_fw, "fw_src": fw_src, "bw": no_tune or forced_bw,
+             "launch_bw": launch_bw, "bw_src": bw_src,
+             "fw_choice": max(0, tu0.fw_variant), "bw_choice": max(0, tu0.bw_variant), "fw_log": [], "bw_log": []}
+
+    def timed(launcher, ptrs, device, reps=3):
+        """Median device time of ``reps`` launches after one warm-up launch (which also compiles)."""
+        launcher(ptrs, device)
+        ms = []
+        for _ in range(reps):
+            ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record()
+            launcher(ptrs, device)
+            ev[1].record()
+            ev[1].synchronize()
+            ms.append(ev[0].elapsed_time(ev[1]))
+        return sorted(ms)[len(ms) // 2]
 
     def autotune_backward(ptrs, device, dxs, ds0):
-        """Time the alternative backward tilings once, writing into throw-away
+        """Time the alternative backward kernels once, writing into throw-away
         gradient buffers (the kernel accumulates into some of its outputs)."""
         tuned["bw"] = True
         nouts = len(dxs) + len(ds0)
         first_out = len(ptrs) - 1 - nouts
         scratch = [th.zeros_like(t) for t in list(ds0) + list(dxs)]
         trial = list(ptrs[:first_out]) + [t.data_ptr() for t in scratch] + [ptrs[-1]]
-        best = None
-        for tile in backward_tile_candidates(plan):
+        best, log = None, []
+        for k, kw in enumerate(backward_variants(plan)):
             try:
-                ks = bw_src if tile is plan.bw_tile else generate_backward(plan, tile)
+                ks = bw_src if k == 0 else generate_backward(plan, **kw)
                 if ks is None:
                     continue
-                launcher = launch_bw if tile is plan.bw_tile else make(ks)
-                launcher(trial, device)
-                ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
-                ev[0].record()
-                launcher(trial, device)
-                ev[1].record()
-                ev[1].synchronize()
-                ms = ev[0].elapsed_time(ev[1])
+                launcher = launch_bw if k == 0 else make(ks)
+                ms = timed(launcher, trial, device)
             except (lower.LoweringError, RuntimeError):
                 continue
+            log.append((k, ks.info["tile"], round(ms, 4)))
             if best is None or ms < best[0]:
-                best = (ms, launcher, ks)
+                best = (ms, launcher, ks, k)
         if best is not None:
             tuned["launch_bw"], tuned["bw_src"] = best[1], best[2]
+            tuned["bw_choice"], tuned["bw_log"] = best[3], log
             forward.sources = (tuned["fw_src"], best[2])       # type: ignore[attr-defined]
 
     def autotune_forward(ptrs, device):
-        """Time the alternative forward tilings once on the real arguments (the
+        """Time the alternative forward kernels once on the real arguments (the
         forward kernel only writes its outputs) and keep the fastest."""
         tuned["fw"] = True
-        best = None
-        default_pack = bool(plan.tuning.pack2 & 2)
-        cands = [(tile, default_pack, None) for tile in forward_tile_candidates(plan)]
-        cands.append((plan.fw_tile, not default_pack, None))
-        if plan.reverse is None and plan.D <= 16:
-            # one chunk per checkpoint interval, step loop fully unrolled (Gated Delta: 9 % faster forward)
-            cands.append((plan.fw_tile, default_pack, plan.D))
-        for tile, pack, chunk in cands:
+        best, log = None, []
+        for k, kw in enumerate(forward_variants(plan)):
             try:
-                planned = tile is plan.fw_tile and pack == default_pack and chunk is None
-                ks = fw_src if planned else generate_forward(plan, tile, pack, stage=chunk, unroll=chunk)
-                launcher = launch_fw if planned else make(ks)
-                launcher(ptrs, device)                                   # compile + warm up
-                ev = [th.cuda.Event(enable_timing=True) for _ in range(2)]
-                ev[0].record()
-                for _ in range(2):
-                    launcher(ptrs, device)
-                ev[1].record()
-                ev[1].synchronize()
-                ms = ev[0].elapsed_time(ev[1]) / 2
+                ks = fw_src if k == 0 else generate_forward(plan, **kw)
+                launcher = launch_fw if k == 0 else make(ks)
+                ms = timed(launcher, ptrs, device)
             except (lower.LoweringError, RuntimeError):
                 continue
-            if "spill stores" in getattr(launcher, "log", "") and " 0 bytes spill stores" not in launcher.log:
-                ms *= 1.0    # spilling variants compete on time like the others
+            log.append((k, ks.info["tile"], bool(ks.info["packed"]), round(ms, 4)))
             if best is None or ms < best[0]:
-                best = (ms, launcher, ks)
+                best = (ms, launcher, ks, k)
         if best is not None:
             tuned["launch_fw"], tuned["fw_src"] = best[1], best[2]
+            tuned["fw_choice"], tuned["fw_log"] = best[3], log
             forward.sources = (best[2], tuned["bw_src"])       # type: ignore[attr-defined]
 
     def forward(inputs_, state0):
@@ -697,6 +774,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         check_align(state0, st_align, "initial state")
         device = inputs_[0].device
         with _device_ctx(device):
+            check_before(device)
             outs = tuple(th.empty(p.B, p.T, p.H, p.M, dtype=d, device=device)
                          for d in [o[2] for o in fw_meta[:nout]])
             stT = tuple(th.empty_like(s) for s in state0)
@@ -720,6 +798,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         aux = aux_[0] if isinstance(aux_, (tuple, list)) else aux_
         device = inputs_[0].device
         with _device_ctx(device):
+            check_before(device)
             dxs = []
             for go, x in zip(plan.grads, inputs_):
                 if go.atomic:
@@ -745,12 +824,14 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
     def kernel_status(device=None) -> int:
         """Error word the kernels write on a timed-out wait (0 = none). Synchronises."""
         device = th.device(device) if device is not None else dev
-        if device.index not in err_words:
-            return 0
-        return int(err_words[device.index].item())
+        if emulated:
+            return int(emu_words["w"].item()) if "w" in emu_words else 0
+        idx = device.index if device.index is not None else th.cuda.current_device()
+        return int(_status[idx].word.item()) if idx in _status else 0
 
     forward.plan = plan                     # type: ignore[attr-defined]
     forward.sources = (fw_src, bw_src)      # type: ignore[attr-defined]
     forward.launchers = (launch_fw, launch_bw)   # type: ignore[attr-defined]
     forward.kernel_status = kernel_status   # type: ignore[attr-defined]
+    forward.tuned = tuned                   # type: ignore[attr-defined]  (which variants were timed and kept)
     return forward, backward, fw_meta, bw_meta

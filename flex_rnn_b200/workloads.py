@@ -69,114 +69,3 @@ def synthetic(op: str, B: int, T: int, H: int, M: int, N: int, dtype=torch.bfloa
     dy = n(B, T, H, M)
     dS = n(B, H, M, N)
     return [x.to(dtype) for x in xs], dy.to(dtype), dS.to(dtype)
-
-
-# ---------------------------------------------------------------------------
-# Further step families (the other examples of the reference's tests/examples.py,
-# written on [B,T,H,M|1,N|1] inputs directly).  ``zoo_case`` draws small
-# synthetic arguments for each of them; used by the parity tests.
-# ---------------------------------------------------------------------------
-
-def rwkv6(q, k, v, w, u, S):
-    y = ((S + v * (u * k)) * q).sum(-1, True)
-    S = S * w.exp() + v * k
-    return y, S
-
-
-def gla(q, k, v, g, S):
-    S = S * g.exp() + v * k
-    return (S * q).sum(-1, True), S
-
-
-def retention(w, q, k, v, S):
-    S = w * S + v * k
-    return (S * q).sum(-1, True), S
-
-
-def longhorn(u, q, k, dt, S):
-    k2 = k * k
-    dt = 1 / (1 + (-dt).exp() + k2.sum(-1, True))
-    S = S - dt * S * k2 + dt * u * k
-    return (S * q).sum(-1, True), S
-
-
-def rwkv4(w, u, k, v, sa, sb, sc):
-    x = k + u - sc
-    A = (-x * (x > 0)).exp()
-    B = (x * (x < 0)).exp()
-    y = (A * sa + B * v) / (A * sb + B)
-    w = -w.exp()
-    x = k - w - sc
-    A = (-x * (x > 0)).exp()
-    B = (x * (x < 0)).exp()
-    return y, (A * sa + B * v, A * sb + B, k - x * (x < 0))
-
-
-def hgrn(x, g, s):
-    s = g.exp() * s + x
-    return s, s
-
-
-def mamba(u, dt, A, b, c, S):
-    S = (dt * A).exp() * S + (dt * u) * b
-    return (S * c).sum(-1, True), S
-
-
-def s4d(u, Ar, Ai, Qr, Qi, D, Sr, Si):
-    Sr_ = Ar * Sr - Ai * Si + u
-    Si_ = Ar * Si + Ai * Sr
-    y = torch.sum(Sr_ * Qr - Si_ * Qi, dim=-1, keepdim=True) + D * u
-    return y, (Sr_, Si_)
-
-
-def mlstm_gates(i, f, sc):
-    f = -torch.log(1 + torch.exp(-f))
-    m = f + sc
-    sc_ = m + (i - m) * (i > m).float()
-    return ((i - sc_).exp(), (f + sc - sc_).exp(), sc_), sc_
-
-
-ZOO = {"rwkv6": rwkv6, "gla": gla, "retention": retention, "longhorn": longhorn, "rwkv4": rwkv4, "hgrn": hgrn,
-       "mamba": mamba, "s4d": s4d, "mlstm_gates": mlstm_gates}
-
-
-def zoo_case(op: str, B: int, T: int, H: int, M: int, N: int, dtype=torch.float32, seed: int = 0):
-    """(inputs, states) of a step family of ``ZOO`` at the given sizes."""
-    g = torch.Generator().manual_seed(seed)
-    n = lambda *s: torch.randn(*s, generator=g)
-    row, col, sc = (lambda: n(B, T, H, 1, N)), (lambda: n(B, T, H, M, 1)), (lambda: n(B, T, H, 1, 1))
-    if op == "rwkv6":
-        ins = [row(), row(), col(), -torch.sigmoid(row()), n(1, 1, H, 1, N)]
-        sts = [n(B, H, M, N)]
-    elif op == "gla":
-        ins = [row(), row(), col(), -torch.sigmoid(row())]
-        sts = [n(B, H, M, N)]
-    elif op == "retention":
-        w = (1 - 2.0 ** (-5 - torch.arange(H).float())).view(1, 1, H, 1, 1).expand(B, T, H, 1, 1).contiguous()
-        ins = [w, row(), row(), col()]
-        sts = [n(B, H, M, N)]
-    elif op == "longhorn":
-        ins = [col(), row(), row(), col()]
-        sts = [torch.zeros(B, H, M, N)]
-    elif op == "rwkv4":
-        s = n(B, 3, H, M, 1)
-        s[:, 2] = -1e30
-        ins = [n(1, 1, H, M, 1), n(1, 1, H, M, 1), col(), col()]
-        sts = [s[:, 0].contiguous(), s[:, 1].contiguous(), s[:, 2].contiguous()]
-    elif op == "hgrn":
-        ins = [col(), -torch.sigmoid(col())]
-        sts = [torch.zeros(B, H, M, 1)]
-    elif op == "mamba":
-        ins = [col(), torch.sigmoid(col()), -torch.sigmoid(n(1, 1, H, M, N)), row(), row()]
-        sts = [torch.zeros(B, H, M, N)]
-    elif op == "s4d":
-        # |Ar + i Ai| < 1: a stable (decaying) diagonal system
-        ins = [col(), 0.65 * torch.rand(1, 1, H, M, N, generator=g), 0.65 * torch.rand(1, 1, H, M, N, generator=g),
-               n(1, 1, H, M, N), n(1, 1, H, M, N), n(1, 1, H, M, 1)]
-        sts = [torch.zeros(B, H, M, N), torch.zeros(B, H, M, N)]
-    elif op == "mlstm_gates":
-        ins = [sc(), sc()]
-        sts = [n(B, H, 1, 1)]
-    else:
-        raise KeyError(op)
-    return [x.to(dtype) for x in ins], [s.to(dtype) for s in sts]

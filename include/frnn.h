@@ -45,6 +45,11 @@ int frnn_abi_version(void);
 /* Message for the calling thread's most recent failure ("" if none). */
 const char* frnn_last_error(void);
 
+/* Version of the NVRTC that frnn_compile uses (12, 8 for NVRTC 12.8).  A cubin
+ * cache must key on it: the reference keys its build directory on the source
+ * hash alone (flex_rnn/to_cuda.py:264) and relies on ninja to rebuild. */
+int frnn_nvrtc_version(int* major, int* minor);
+
 /*
  * Compile CUDA C++ `src` to an sm_100a cubin with NVRTC (no GPU needed).
  * Replaces the nvcc+ninja build of flex_rnn/to_cuda.py:274-279.
@@ -95,6 +100,31 @@ int frnn_launch(frnn_module_t m, int kernel, const unsigned grid[3], const unsig
 int frnn_tensor_map_encode(void* out_map, const void* base, unsigned elt_bytes, unsigned rank,
                            const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
 
+/*
+ * Kernel error word.  Every device-side wait of the generated kernels is
+ * time-bounded; a kernel whose wait ran out writes a non-zero code into the
+ * `int` error word it was given as its last pointer parameter and returns
+ * early, so its outputs are not valid.  (The reference has no counterpart: its
+ * stubs check nothing, flex_rnn/to_cuda.py:245-252.)  The word is sticky until
+ * one of the calls below clears it.
+ *
+ * frnn_status:       copies the word to the host on `stream`, waits for the
+ *                    stream, and returns FRNN_E_KERNEL (word cleared, message
+ *                    in frnn_last_error) if it was non-zero.  Synchronises.
+ * frnn_status_post:  enqueues the copy of the word into `host_word` (pinned
+ *                    host memory for a truly asynchronous copy) behind the
+ *                    launches already on `stream`.  Does not wait.
+ * frnn_status_check: looks at `host_word` as it is now, without waiting: 0 ->
+ *                    FRNN_OK; otherwise clears `host_word`, enqueues a clear of
+ *                    `err_word_dev` (may be NULL) on `stream` and returns
+ *                    FRNN_E_KERNEL.  Called at the start of the next operation
+ *                    it reports what the previous launches left, at no cost on
+ *                    the hot path.
+ */
+int frnn_status(int* err_word_dev, void* stream);
+int frnn_status_post(int* err_word_dev, int* host_word, void* stream);
+int frnn_status_check(int* host_word, int* err_word_dev, void* stream);
+
 /* Registers per thread, static shared bytes and local (spill) bytes per thread
  * of a loaded kernel, as the driver reports them. */
 int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, int* local_bytes);
@@ -118,7 +148,8 @@ int frnn_kernel_attrs(frnn_module_t m, int kernel, int* regs, int* static_smem, 
  * Limits and rules:
  *  - the slices together must fit frnn_static_scratch_capacity() bytes
  *    (32 MiB); a larger request fails with FRNN_E_ARG and launches nothing;
- *  - at most 64 kernel parameters;
+ *  - at most 64 kernel parameters; `nscratch` may not exceed `nargs` and no
+ *    parameter index may be listed twice (FRNN_E_ARG otherwise);
  *  - every GPU on which the library is used keeps the array until the process
  *    exits; all calls on a device share it and it keeps the previous call's
  *    contents, so a kernel must not expect zeros there (the forward kernels

@@ -125,3 +125,27 @@ def test_sizes_that_are_not_powers_of_two(op, M, N):
     y, ST, store, aux = fwd(tuple(xs[:-1]), (xs[-1],))
     dx, ds0 = bwd((dy,), (dS,), tuple(xs[:-1]), (store,), (aux,))
     check(op, xs, dy, dS, (y, ST, list(dx) + list(ds0)), 1e-5, 1e-5)
+
+
+@pytest.mark.parametrize("dim", [0, 1, 2])
+def test_expanded_input(dim):
+    """An input expanded (stride 0) over the batch, time or head dimension is
+    read with its own strides: no tiled tensor map is built for it (a map would
+    need a real byte stride for that dimension), it takes the per-timestep bulk
+    copies instead, and its gradient has the full shape."""
+    B, T, H, M, N = 2, 6, 2, 16, 16
+    xs, dy, dS = O.make_case("delta_rule", B, T, H, M, N, torch.float32)
+    shape = list(xs[0].shape)
+    shape[dim] = 1
+    g = torch.Generator().manual_seed(11)
+    small = torch.nn.functional.normalize(torch.randn(shape, generator=g), dim=-1)
+    xs[0] = small.expand(B, T, H, 1, N)
+    assert xs[0].stride(dim) == 0
+    fwd, bwd, _, _ = build_twopass(W.delta_rule, tuple(xs[:-1]), (xs[-1],), tuning=SMALL, _launcher=EmuLauncher)
+    for ks in fwd.sources:
+        assert all(tm["src"] != "in0" for tm in ks.tmaps)
+        assert ks.info["tma_items"] > 0
+    y, ST, store, aux = fwd(tuple(xs[:-1]), (xs[-1],))
+    dx, ds0 = bwd((dy,), (dS,), tuple(xs[:-1]), (store,), (aux,))
+    dense = [x.contiguous() for x in xs]
+    check("delta_rule", dense, dy, dS, (y, ST, list(dx) + list(ds0)), 1e-5, 1e-5)

@@ -203,3 +203,24 @@ def test_more_ctas_than_sms_small_state(op_name):
                 continue                        # summed over the batch: not a per-slice quantity
             gs = g[b:b + 1, :, h:h + 1] if x.dim() == 5 else g[b:b + 1, h:h + 1]
             assert O.rel_err(gs, r) < 1e-5, (op_name, b, h)
+
+
+def test_examples_cli_and_benchmark(capsys):
+    """The user-facing tooling runs: the examples command line (as a fresh
+    process, check mode: compiled op against naive_fp64 with the reference's
+    1e-2 acceptance), its benchmark mode, and one direct ``benchmark()`` call."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "flex_rnn_b200.examples", "--op", "delta_rule", "--check-flex", "--seqlen", "64"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "Verifying flex compiled kernel" in r.stdout and "Gradient rel. errors" in r.stdout
+    from flex_rnn_b200 import examples
+    examples.main(["--op", "hgrn", "--benchmark-flex", "--seqlen", "64", "--batchsz", "2", "--modeldim", "256"])
+    out = capsys.readouterr().out
+    assert "Benchmarking flex compiled kernel" in out and " ms (" in out and "memory" in out
+    xs, _, _ = O.make_case("mamba2", 2, 32, 2, 64, 64, torch.float32)
+    op = flex_rnn_b200.jit(O.mamba2)
+    ms = flex_rnn_b200.benchmark(op, [x.to(DEV) for x in xs], warmup=2, rep=5, verbose=False)
+    assert 0.0 < ms < 1e3

@@ -3,6 +3,7 @@ import pytest
 import torch
 
 import flex_rnn_b200
+from flex_rnn_b200 import examples as X
 from flex_rnn_b200 import workloads as W
 from flex_rnn_b200.graph import MN, M1, N1, S11, UnsupportedStepOp
 from flex_rnn_b200.lower import LoweringError, choose_tile
@@ -185,6 +186,6 @@ def test_dry_run_under_fake_tensors():
         fm, bm = build_twopass(W.delta_rule, (q, q, v, b), (torch.empty(2, 3, 8, 16, **bf),), dryrun=True)
         assert tuple(fm[0][0]) == (2, 7, 3, 8) and fm[0][2] == torch.bfloat16 and tuple(bm[-1][0]) == (2, 3, 8, 16)
         i = torch.empty(2, 7, 3, 1, 1, device="cuda")
-        fm, bm = build_twopass(W.mlstm_gates, (i, i), (torch.empty(2, 3, 1, 1, device="cuda"),), dryrun=True)
+        fm, bm = build_twopass(X.mlstm_gates, (i, i), (torch.empty(2, 3, 1, 1, device="cuda"),), dryrun=True)
         assert [tuple(m[0]) for m in fm[:4]] == [(2, 7, 3, 1)] * 3 + [(2, 3, 1, 1)]
         assert [tuple(m[0]) for m in bm] == [(2, 7, 3, 1, 1)] * 2 + [(2, 3, 1, 1)]

@@ -16,6 +16,7 @@ import pytest
 import torch
 
 from flex_rnn_b200 import lower
+from flex_rnn_b200 import examples as X
 from flex_rnn_b200 import workloads as W
 from flex_rnn_b200.twopass import Tuning, build_twopass
 from oracle import naive_oracle as O
@@ -68,12 +69,12 @@ def draw_case(rng: random.Random):
         ins = [col(), torch.nn.functional.softplus(-1 + sc()), -torch.exp(n(1, 1, H, 1, 1)), row() / N ** .5, row() / N ** .5]
         sts = [torch.zeros(B, H, M, N)]
     elif fam == "gla":
-        step, ins, sts = W.gla, [row(), row(), col(), -torch.sigmoid(row())], [n(B, H, M, N)]
+        step, ins, sts = X.gla, [row(), row(), col(), -torch.sigmoid(row())], [n(B, H, M, N)]
     elif fam == "retention":
-        step, ins, sts = W.retention, [torch.sigmoid(sc()), row(), row(), col()], [n(B, H, M, N)]
+        step, ins, sts = X.retention, [torch.sigmoid(sc()), row(), row(), col()], [n(B, H, M, N)]
     elif fam == "hgrn":
         N = 1
-        step, ins, sts = W.hgrn, [n(*bc([B, T, H, M, 1])), -torch.sigmoid(n(*bc([B, T, H, M, 1])))], [n(B, H, M, 1)]
+        step, ins, sts = X.hgrn, [n(*bc([B, T, H, M, 1])), -torch.sigmoid(n(*bc([B, T, H, M, 1])))], [n(B, H, M, 1)]
     elif fam == "two_outputs":
         step, ins, sts = two_outputs, [row(), row(), col(), torch.sigmoid(row())], [n(B, H, M, N)]
     elif fam == "two_states":

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import flex_rnn_b200
+from flex_rnn_b200 import examples as X
 from flex_rnn_b200 import workloads as W
 from flex_rnn_b200.twopass import Tuning, build_twopass
 from oracle import naive_oracle as O
@@ -19,16 +20,16 @@ def shapes(op):
 
 
 def oracle(op, ins, sts, dys, dSs):
-    return O.fwd_bwd(W.ZOO[op], ins, sts, dys, dSs, dtype=torch.float64)
+    return O.fwd_bwd(X.ZOO[op], ins, sts, dys, dSs, dtype=torch.float64)
 
 
 @pytest.mark.parametrize("op", ["rwkv6", "rwkv4", "s4d", "longhorn"])
 def test_emulated(op):
     from emu.emu import EmuLauncher
     M, N = shapes(op)
-    ins, sts = W.zoo_case(op, 2, 7, 2, M, N)
+    ins, sts = X.zoo_case(op, 2, 7, 2, M, N)
     tu = Tuning(fw_r=2, fw_c=4, fw_mb=16, fw_stage=4, bw_r=2, bw_c=4, seg=2, nslots=2)
-    fwd, bwd, _, _ = build_twopass(W.ZOO[op], tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
+    fwd, bwd, _, _ = build_twopass(X.ZOO[op], tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
     res = fwd(tuple(ins), tuple(sts))
     ns = len(sts)
     no = len(res) - 2 * ns - 1
@@ -49,12 +50,12 @@ def test_emulated_small_state(op, M, N):
     kernels on repeated rows; three outputs for the mLSTM gates."""
     from emu.emu import EmuLauncher
     from flex_rnn_b200.twopass import verify_meta
-    ins, sts = W.zoo_case(op, 2, 7, 2, M, N)
+    ins, sts = X.zoo_case(op, 2, 7, 2, M, N)
     tu = Tuning(fw_r=2, fw_c=4, fw_mb=16, fw_stage=4, bw_r=2, bw_c=4, seg=2, nslots=2)
-    fwd, bwd, fm, bm = build_twopass(W.ZOO[op], tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
+    fwd, bwd, fm, bm = build_twopass(X.ZOO[op], tuple(ins), tuple(sts), tuning=tu, _launcher=EmuLauncher)
     assert fwd.padded_rows % M == 0 and fwd.padded_rows > M
     meta = tuple(x.to("meta") for x in ins), tuple(s.to("meta") for s in sts)
-    assert build_twopass(W.ZOO[op], *meta, dryrun=True) == (fm, bm)
+    assert build_twopass(X.ZOO[op], *meta, dryrun=True) == (fm, bm)
     res = fwd(tuple(ins), tuple(sts))
     ns = len(sts)
     no = len(res) - 2 * ns - 1
@@ -94,14 +95,14 @@ def test_emulated_one_row_or_column_state(M, N):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("op", list(W.ZOO))
+@pytest.mark.parametrize("op", list(X.ZOO))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gpu(op, dtype):
     M, N = (256, 1) if op in ("rwkv4", "hgrn") else (1, 1) if op == "mlstm_gates" else (64, 64)
-    ins, sts = W.zoo_case(op, 2, 40, 3, M, N, dtype)
+    ins, sts = X.zoo_case(op, 2, 40, 3, M, N, dtype)
     dev = "cuda:0"
     leaves = [x.to(dev).requires_grad_() for x in ins + sts]
-    f = flex_rnn_b200.jit(W.ZOO[op])
+    f = flex_rnn_b200.jit(X.ZOO[op])
     outs = f(*leaves)
     g = torch.Generator().manual_seed(1)
     ups = [torch.randn(o.shape, generator=g) for o in outs]
@@ -146,7 +147,7 @@ def _mlstm_steps():
     def step3(q, k, v, i, f, norm, sa):
         sa_ = f * sa + i * v * k
         return (norm * q * sa_).sum(-1, True), sa_
-    return W.mlstm_gates, step2, step3
+    return X.mlstm_gates, step2, step3
 
 
 def _gsa(step1, step2, q, k, v, x, g, sa, sb):

@@ -79,4 +79,21 @@ def test_static_scratch_matches_caller_allocated_scratch():
         ptrs += tensor_maps(ptrs)
         with pytest.raises(runtime.FrnnError, match="more scratch than the library's static buffer"):
             mod.launch_static_scratch(0, fw.grid, fw.block, fw.smem_bytes, stream, ptrs, {i_ck: cap, i_aux: 4096})
+
+        # a scratch list longer than the parameter list, or naming a parameter twice, is refused too
+        import ctypes
+        n = len(ptrs)
+        vals = (ctypes.c_void_p * n)(*[0 if isinstance(p, runtime.StructArg) else int(p) for p in ptrs])
+        args = (ctypes.c_void_p * n)(*[p.addr if isinstance(p, runtime.StructArg) else ctypes.addressof(vals) + 8 * i
+                                       for i, p in enumerate(ptrs)])
+        g = (ctypes.c_uint * 3)(*fw.grid)
+        b = (ctypes.c_uint * 3)(fw.block, 1, 1)
+        lib = runtime.lib()
+        for idx in ([i_ck, i_ck], list(range(n)) + [0]):
+            sa = (ctypes.c_int * len(idx))(*idx)
+            sb = (ctypes.c_size_t * len(idx))(*([256] * len(idx)))
+            rc = lib.frnn_launch_static_scratch(mod._h, 0, g, b, fw.smem_bytes, ctypes.c_void_p(stream), args, n, sa, sb, len(idx))
+            assert rc == 1, lib.frnn_last_error()
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
         mod.close()
