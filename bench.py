@@ -12,22 +12,29 @@ workload on its own batch shard: the (b,h) recurrences are independent, so
 there is no collective in the timed region ("weak" scaling); the only NCCL
 calls are the barriers and the max-reduction of the timings.
 
-Printed JSON (rank 0): tokens/s of the whole job with inputs resident in HBM
-(`value`), the same through the public API with pinned host buffers and
-host<->device copies in the timed region (`e2e`), the roofline record of the
-dominant kernel (the backward scan; bound = FP32 CUDA-core pipe, peak measured
-in-run by an FMA-only probe kernel), and the CPU oracle timed on a bounded
-sample (`cpu_baseline`).
+Printed JSON (rank 0), one line:
+  value / ms_per_step   tokens/s of the whole job with inputs resident in HBM
+  e2e                   the same through the public API with pinned host buffers
+                        and host<->device copies in the timed region
+  roofline              the dominant kernel (the backward scan): bound = FP32
+                        CUDA-core pipe, peak measured in-run by an FMA-only probe
+  cpu_baseline          the reference's CPU path (its jit.naive + autograd) on a
+                        bounded sample, on the host cores (one GPU only)
+  workloads             (one GPU) the other benchmark configurations - RWKV-7,
+                        Mamba-2, Gated Delta Rule at B8 T1024 - timed the same way
+  scaling_c4            the scaling configuration: Gated Delta Rule, global batch
+                        64, T4096, split over the N GPUs by ``shard.shard_args``
+                        ("strong" scaling: total work fixed)
+  reference_cuda        (one GPU) the unmodified reference package's own generated
+                        CUDA kernels on the same GPU and inputs, when an install
+                        of it is present under baseline/_ref
 
-`--impl reference` times the CPU oracle (the restatement of the reference's
-`jit.naive` + autograd, which is the reference's only CPU implementation of
-this path) on a bounded sample of the same workload, on all host threads.
+`--impl reference` times the reference's CPU implementation of the path on the
+host cores: `jit.naive` of the reference package itself when an install of it is
+importable from `baseline/_ref` (kind "reference"), else the restatement in
+`oracle/` (kind "port"); one batch element, all heads, per step.
 
-`--impl reference_cuda` times the unmodified reference package's own generated
-CUDA kernels (through its `jit` object) on the same GPU, workload and inputs,
-when an install of it is present under `baseline/_ref` (not part of this
-repository); otherwise it prints an `unavailable` line.  It is the GPU kernel
-this backend replaces, reported beside the CPU baseline.
+`--impl reference_cuda` is the arm behind the `reference_cuda` record.
 """
 import argparse
 import json
@@ -42,22 +49,24 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (oracle step name, B, T, H, M, N)
+    # name: (step name, B, T, H, M, N)
     "delta_rule": ("delta_rule", 8, 1024, 32, 128, 128),
     "rwkv7": ("rwkv7", 8, 1024, 32, 128, 128),
     "mamba2": ("mamba2", 8, 1024, 32, 64, 128),
     "gated_delta_rule": ("gated_delta_rule", 8, 1024, 32, 128, 128),
-    # the scaling configuration: a global batch of 64 sequences of 4096 steps split over the GPUs ("strong" scaling;
-    # 8 sequences per GPU at 8 GPUs, all 64 on one: about 90 GB of checkpoints, row sums and I/O)
+    # the scaling configuration: a global batch of 64 sequences of 4096 steps split over the GPUs
     "gated_delta_rule_c4": ("gated_delta_rule", 64, 4096, 32, 128, 128),
 }
 STRONG = ("gated_delta_rule_c4",)
-# DRAM bytes (read + write) of one backward launch per (batch, head) pair, from the ncu capture summarised in
-# profiles/*_b2_frnn_fw_bw_ncu_full.md (B=2, 64 pairs; Delta Rule 204.0 MB); traffic grows with the pair count
-NCU_BW_DRAM_BYTES_PER_BH = {"delta_rule": 204.03e6 / 64, "rwkv7": 782.1e6 / 64, "mamba2": 355.5e6 / 64,
-                            "gated_delta_rule": 690.5e6 / 64}
+# per-element op counts of the joint graphs as the reference's tracer yields them (scalars expanded to rows);
+# this backend keeps scalars as scalars, which makes Mamba-2's executed graph three ops shorter
+K_JOINT_REFERENCE_TRACER = {"delta_rule": 18, "rwkv7": 28, "mamba2": 19, "gated_delta_rule": 22}
 METRIC = "fwd+bwd tokens/s"
 UNIT = "tokens/s"
+
+
+def workload_text(op, B, T, H, M, N):
+    return f"{op} fwd+bwd, B{B} T{T} H{H} {M}x{N} per GPU, bf16 I/O, fp32 state and math"
 
 
 class ClockSampler:
@@ -105,11 +114,36 @@ def bytes_io(tensors):
     return sum(t.numel() * t.element_size() for t in tensors)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# CPU legs: the reference's jit.naive + autograd on the host cores
+# ---------------------------------------------------------------------------------------------------------------
+
+_REF_JIT = {}
+
+
+def reference_naive(step_fn):
+    """(callable running the reference's own ``jit.naive`` for ``step_fn``, "reference"), from an install of the
+    reference package under baseline/_ref; or (None, why) when there is none."""
+    if "mod" not in _REF_JIT:
+        ref_dir = os.path.join(ROOT, "baseline", "_ref")
+        try:
+            if not os.path.isdir(os.path.join(ref_dir, "flex_rnn")):
+                raise ImportError("no reference install under baseline/_ref")
+            sys.path.insert(0, ref_dir)
+            import flex_rnn
+            _REF_JIT["mod"] = flex_rnn
+        except Exception as e:      # not part of this repository: fall back to the port
+            _REF_JIT["mod"] = None
+            _REF_JIT["why"] = f"{type(e).__name__}: {str(e)[:120]}"
+    if _REF_JIT["mod"] is None:
+        return None, _REF_JIT["why"]
+    return _REF_JIT["mod"].jit(step_fn).naive, "reference"
+
+
 def cpu_sample(opname, B, T, H, M, N, heads=None):
-    """Times the CPU oracle (fwd + autograd bwd) on a (b,h) sub-slice of the
-    workload and scales to whole-workload tokens/s (the slices are independent
-    recurrences of equal cost).  ``heads``: heads of one batch element in the
-    sample (default: all of them, about ten seconds of CPU work)."""
+    """Times the reference's CPU path (fwd + autograd bwd) on a (b,h) sub-slice of the workload and scales to
+    whole-workload tokens/s (the slices are independent recurrences of equal cost).  ``heads``: heads of one batch
+    element in the sample (default: all of them, under a second to a few seconds of CPU work)."""
     import torch
     from oracle import naive_oracle as O
     # all the host threads this process may use (a launcher such as torch.distributed.run pins OMP_NUM_THREADS to 1)
@@ -119,25 +153,37 @@ def cpu_sample(opname, B, T, H, M, N, heads=None):
         pass
     sb, sh = 1, min(H, heads or H)
     xs, dy, dS = O.make_case(opname, sb, T, sh, M, N, torch.bfloat16)
+    naive, kind = reference_naive(O.STEPS[opname])
     t0 = time.perf_counter()
-    O.fwd_bwd(O.STEPS[opname], xs[:-1], xs[-1:], [dy], [dS])
+    if naive is not None:
+        leaves = [x.detach().clone().requires_grad_() for x in xs]
+        y, ST = naive(*leaves)
+        torch.autograd.grad([y, ST], leaves, [dy.to(y.dtype), dS.to(ST.dtype)], allow_unused=True)
+        what = "the reference's jit.naive (baseline/_ref)"
+    else:
+        O.fwd_bwd(O.STEPS[opname], xs[:-1], xs[-1:], [dy], [dS])
+        kind, what = "port", "oracle restatement of jit.naive"
     dt = time.perf_counter() - t0
     frac = (sb * sh) / (B * H)
-    return {"value": B * T * frac / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"oracle naive fwd+autograd bwd on B={sb},H={sh} of the B={B},H={H} workload "
+    return {"value": B * T * frac / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{what} fwd + autograd bwd on B={sb},H={sh} of the B={B},H={H} workload "
                       f"(T={T}, {M}x{N}, bf16 inputs, fp32 math), {dt:.2f} s, scaled by {1 / frac:.0f}x"}, dt
+
+
+def cpu_heads(H, T, n_passes):
+    """Heads of one batch element per pass: all of them for the headline sizes (the same sample in the
+    `cpu_baseline` record and in the reference arm), fewer only when many passes or long sequences are asked for."""
+    per_head = 0.03 * T / 1024
+    return next((h for h in (H, 16, 8, 4, 2, 1) if h <= H and per_head * h * n_passes <= 240), 1)
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    import torch
     opname, B, T, H, M, N = WORKLOADS[args.op]
-    # size the per-step sample so that the whole run stays within a few minutes (about 0.25 s per head)
     n = max(1, args.warmup + args.steps)
-    heads = next((h for h in (32, 16, 8, 4, 2, 1) if h <= H and 0.25 * h * n <= 150), 1)
-    times = []
-    base = None
+    heads = cpu_heads(H, T, n)
+    times, base = [], None
     for i in range(args.warmup + args.steps):
         base, dt = cpu_sample(opname, B, T, H, M, N, heads)
         if i >= args.warmup:
@@ -149,12 +195,16 @@ def run_reference(args, rank, world):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp32", "data": "synthetic",
-            "config": {"workload": f"{args.op} B{B} T{T} H{H} {M}x{N} bf16 I/O (bounded CPU sample per step)"},
+            "config": {"workload": workload_text(args.op, B, T, H, M, N)},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
+
+# ---------------------------------------------------------------------------------------------------------------
+# the reference's own CUDA path (third arm)
+# ---------------------------------------------------------------------------------------------------------------
 
 def run_reference_cuda(args, rank, world, local):
     """fwd+bwd of the reference package's own compiled path, timed like the main arm (device events, max over ranks)."""
@@ -189,6 +239,8 @@ def run_reference_cuda(args, rank, world, local):
                 dist.barrier()
         for _ in range(max(args.warmup, 3)):
             step()
+        torch.cuda.synchronize(dev)
+        torch.cuda.reset_peak_memory_stats(dev)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
         times = []
         for _ in range(args.steps):
@@ -199,6 +251,7 @@ def run_reference_cuda(args, rank, world, local):
             e1.record()
             torch.cuda.synchronize(dev)
             times.append(e0.elapsed_time(e1))
+        peak_gib = (torch.cuda.max_memory_allocated(dev) - flush.numel()) / 2 ** 30
         ms = torch.tensor([sum(times) / len(times)], device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -208,11 +261,379 @@ def run_reference_cuda(args, rank, world, local):
             print(json.dumps({"impl": "reference_cuda", "metric": METRIC, "value": world * B * T / (ms / 1e3), "unit": UNIT,
                               "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
                               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-                              "config": {"workload": f"{args.op} B{B} T{T} H{H} {M}x{N} bf16 I/O, fp32 math, per GPU",
+                              "peak_memory_gib": round(peak_gib, 3),
+                              "config": {"workload": workload_text(args.op, B, T, H, M, N),
                                          "l2": "256 MiB flush write between timed steps"}}), flush=True)
     except Exception as e:  # the reference is not part of this repository: report, do not fail
         if rank == 0:
             print(json.dumps({"impl": "reference_cuda", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}), flush=True)
+
+
+def reference_cuda_record(op, steps):
+    """Runs the `--impl reference_cuda` arm in a process of its own (the reference compiles an extension with nvcc
+    and ninja on first use) and returns its JSON record."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference_cuda", "--op", op, "--steps", str(steps), "--warmup", "3"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        for ln in reversed(r.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+        return {"impl": "reference_cuda", "unavailable": f"no record (exit {r.returncode}): {r.stderr[-200:]}"}
+    except Exception as e:
+        return {"impl": "reference_cuda", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# this backend
+# ---------------------------------------------------------------------------------------------------------------
+
+class Bench:
+    def __init__(self, args, rank, world, local):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.args, self.rank, self.world, self.local = args, rank, world, local
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+        torch.cuda.set_device(local)
+        self.dev = torch.device("cuda", local)
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.stream = torch.cuda.current_stream(self.dev)
+        self.sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        self.peaks = {}
+        try:
+            self.peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        self.hbm = self.peaks.get("hbm_gbs", 6650.0)
+        self.fp32_peak = None
+
+    def sync_all(self):
+        self.torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, x):
+        t = self.torch.tensor([float(x)], device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def probe_fp32_peak(self):
+        """FP32 CUDA-core peak, measured now with the library's FMA-only probe kernel."""
+        from flex_rnn_b200 import runtime
+        torch = self.torch
+        sink = torch.zeros(4, device=self.dev)
+        probe = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            fl = runtime.fp32_peak_probe(sink.data_ptr(), 20000, self.stream.cuda_stream)
+            e1.record(self.stream)
+            torch.cuda.synchronize(self.dev)
+            probe.append(fl / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        self.fp32_peak = max(probe[1:])
+        return self.fp32_peak
+
+    # ---- one workload, inputs resident in HBM -------------------------------------------------------------
+    def measure(self, opname, xs, dy, dS, steps, warmup, sample_clocks=False):
+        """Forward + backward of ``jit(step)`` on device-resident arguments: ``warmup`` untimed steps (the first
+        compiles and autotunes), then ``steps`` timed ones between barriers; device events; max over ranks."""
+        import flex_rnn_b200
+        from flex_rnn_b200 import workloads as W
+        torch = self.torch
+        op = flex_rnn_b200.jit(W.STEPS[opname])
+        leaves = [x.requires_grad_() for x in xs]
+        stream = self.stream
+
+        def one_step(record):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+            if record:
+                ev[0].record(stream)
+            y, ST = op(*leaves)
+            if record:
+                ev[1].record(stream)
+            grads = torch.autograd.grad([y, ST], leaves, [dy, dS])
+            if record:
+                ev[2].record(stream)
+            return ev, grads
+
+        for _ in range(warmup):
+            one_step(False)
+        self.sync_all()
+        assert op.forward_func.kernel_status(self.dev) == 0, "a kernel reported a timed-out wait"
+        torch.cuda.reset_peak_memory_stats(self.dev)
+        sampler = ClockSampler(self.local) if (sample_clocks and self.rank == 0) else None
+        if sampler:
+            sampler.start()
+        self.sync_all()
+        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_start.record(stream)
+        evs = [one_step(True)[0] for _ in range(steps)]
+        t_end.record(stream)
+        self.sync_all()
+        clocks = sampler.stop() if sampler else None
+        total_ms = self.max_over_ranks(t_start.elapsed_time(t_end))
+        fw_ms = [ev[0].elapsed_time(ev[1]) for ev in evs]
+        bw_ms = [ev[1].elapsed_time(ev[2]) for ev in evs]
+        return {"op": op, "ms_per_step": total_ms / steps, "fw_ms": fw_ms, "bw_ms": bw_ms, "clocks": clocks,
+                "peak_memory_gib": torch.cuda.max_memory_allocated(self.dev) / 2 ** 30}
+
+    def analyse(self, opname, m, xs, B, T, H, M, N):
+        """Roofline arithmetic of one measured workload (per GPU)."""
+        plan = m["op"].forward_func.plan
+        fw_src, bw_src = m["op"].forward_func.sources
+        tuned = m["op"].forward_func.tuned
+        elems = B * T * H * M * N
+        elt = xs[0].element_size()
+        in_bytes = bytes_io(xs[:-1])
+        st_bytes = bytes_io(xs[-1:])
+        y_bytes = B * T * H * M * elt
+        # compulsory traffic (no checkpoints, no saved row sums): fwd reads inputs + S0, writes y + S_T;
+        # bwd reads inputs + dy + dS_T, writes the gradients + dS0
+        bytes_fw_alg = in_bytes + st_bytes + y_bytes + st_bytes
+        bytes_bw_alg = in_bytes + y_bytes + st_bytes + in_bytes + st_bytes
+        # what the backward launch actually moves, from the plan: plus saved row sums and fp32 checkpoints read
+        aux_bytes = len(plan.aux) * B * H * T * M * 4
+        ck_bytes = plan.nck * B * H * M * N * 4 * plan.n_st
+        traffic_bw = bytes_bw_alg + aux_bytes + ck_bytes
+        traffic_fw = bytes_fw_alg + aux_bytes + ck_bytes
+        fw_avg, bw_avg = statistics.mean(m["fw_ms"]), statistics.mean(m["bw_ms"])
+        k_bw = plan.k_joint - plan.k_fwd
+        peak = self.fp32_peak
+        t_fp32 = elems * plan.k_joint / (peak * 1e12)
+        t_hbm = (bytes_fw_alg + bytes_bw_alg) / (self.hbm * 1e9)
+        step_s = m["ms_per_step"] * 1e-3
+        rec = {
+            "fw_ms": round(fw_avg, 4), "bw_ms": round(bw_avg, 4), "ms_per_step": round(m["ms_per_step"], 4),
+            "tokens_per_s": self.world * B * T / step_s,
+            "roofline_fraction_step": max(t_fp32, t_hbm) / step_s,
+            "roofline_fraction_fw": elems * plan.k_fwd / (fw_avg * 1e-3) / 1e12 / peak,
+            "roofline_fraction_bw": elems * k_bw / (bw_avg * 1e-3) / 1e12 / peak,
+            "k_joint": plan.k_joint, "k_fwd": plan.k_fwd,
+            "fp32_bound_ms": t_fp32 * 1e3, "hbm_bound_ms": t_hbm * 1e3,
+            "peak_memory_gib": round(m["peak_memory_gib"], 3),
+            "checkpoint_every": plan.D, "backward": "reverse re-step" if plan.reverse else "recompute from slots",
+            "fw_kernel": {"grid": list(fw_src.grid), "block": fw_src.block, "smem": fw_src.smem_bytes,
+                          "tile": fw_src.info["tile"][:2], "packed_fp32x2": fw_src.info["packed"],
+                          "variant": tuned["fw_choice"], "timed_variants": len(tuned["fw_log"])},
+            "bw_kernel": {"grid": list(bw_src.grid), "block": bw_src.block, "smem": bw_src.smem_bytes,
+                          "tile": bw_src.info["tile"][:2], "packed_fp32x2": bw_src.info["packed"],
+                          "variant": tuned["bw_choice"], "timed_variants": len(tuned["bw_log"])},
+        }
+        kref = K_JOINT_REFERENCE_TRACER.get(opname)
+        if kref and kref != plan.k_joint:
+            rec["roofline_fraction_step_reference_tracer_k"] = elems * kref / (peak * 1e12) / step_s
+            rec["k_joint_reference_tracer"] = kref
+        extra = {"bytes_fw_alg": bytes_fw_alg, "bytes_bw_alg": bytes_bw_alg, "traffic_bw": traffic_bw, "traffic_fw": traffic_fw,
+                 "achieved_bw": elems * k_bw / (bw_avg * 1e-3) / 1e12, "flops_bw": elems * k_bw, "bw_name": bw_src.name,
+                 "stream_mb": (traffic_fw + traffic_bw) / 1e6}
+        return rec, extra
+
+    # ---- end to end through the public API with host buffers ---------------------------------------------------
+    def measure_e2e(self, op, xs_host, dy_host, dS_host, n_steps):
+        """Pinned host buffers in, pinned host buffers out, copies inside the timed region.  Three streams, two
+        buffer sets: the host->device copy of step i+1 and the device->host copy of step i-1 run beside the
+        kernels of step i."""
+        torch, dev, stream = self.torch, self.dev, self.stream
+        pin = [x.detach().cpu().pin_memory() for x in xs_host]
+        host_in = pin + [dy_host.pin_memory(), dS_host.pin_memory()]
+        out_host = None
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        dev_in = [[torch.empty_like(p, device=dev) for p in host_in] for _ in range(2)]
+        dev_out = [None, None]
+        ev_in = [torch.cuda.Event() for _ in range(2)]       # inputs of the slot are on the device
+        ev_used = [torch.cuda.Event() for _ in range(2)]     # the kernels are done with the slot's inputs
+        ev_done = [torch.cuda.Event() for _ in range(2)]     # results of the slot are staged
+        ev_out = [torch.cuda.Event() for _ in range(2)]      # results of the slot have reached the host
+
+        def e2e_step(i):
+            nonlocal out_host
+            k = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_used[k])
+                for d_, h_ in zip(dev_in[k], host_in):
+                    d_.copy_(h_, non_blocking=True)
+                ev_in[k].record(s_in)
+            stream.wait_event(ev_in[k])
+            stream.wait_event(ev_out[k])
+            d = [t.detach().requires_grad_() for t in dev_in[k][:-2]]
+            y, ST = op(*d)
+            grads = torch.autograd.grad([y, ST], d, [dev_in[k][-2], dev_in[k][-1]])
+            res = [y, ST, *grads]
+            if dev_out[k] is None:
+                dev_out[k] = [torch.empty_like(r) for r in res]
+            if out_host is None:
+                out_host = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
+            for o_, r in zip(dev_out[k], res):
+                o_.copy_(r.detach())
+            ev_used[k].record(stream)
+            ev_done[k].record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[k])
+                for h, o_ in zip(out_host, dev_out[k]):
+                    h.copy_(o_, non_blocking=True)
+                ev_out[k].record(s_out)
+
+        for i in range(4):
+            e2e_step(i)
+        self.sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n_steps):
+            e2e_step(i)
+        stream.wait_stream(s_out)          # the last results must have reached the host
+        stream.wait_stream(s_in)
+        e1.record(stream)
+        self.sync_all()
+        ms = self.max_over_ranks(e0.elapsed_time(e1) / max(1, n_steps))
+        h2d = sum(p.numel() * p.element_size() for p in host_in)
+        d2h = sum(h.numel() * h.element_size() for h in out_host)
+        return ms, h2d, d2h
+
+    # ---- the scaling configuration ---------------------------------------------------------------------------------
+    def scaling_c4(self, steps):
+        """Gated Delta Rule, global batch 64, T4096 ("strong" scaling): every rank draws the same global batch on its
+        GPU, keeps the rows ``shard.shard_args`` assigns to it and runs the single-GPU op on them; no collective."""
+        from flex_rnn_b200 import shard
+        from flex_rnn_b200 import workloads as W
+        torch = self.torch
+        opname, GB, T, H, M, N = WORKLOADS["gated_delta_rule_c4"]
+        # the global batch, drawn on the device (same seed, hence the same values, on every rank), then cut
+        xs_g, dy_g, dS_g = W.synthetic(opname, GB, T, H, M, N, torch.bfloat16, seed=1000, device=self.dev)
+        ins, sts, (lo, hi) = shard.shard_args(xs_g[:-1], xs_g[-1:], self.rank, self.world)
+        own = (lambda t: t) if self.world == 1 else (lambda t: t.contiguous().clone())
+        xs = [own(t) for t in list(ins) + list(sts)]
+        dy, dS = own(dy_g[lo:hi]), own(dS_g[lo:hi])
+        del xs_g, dy_g, dS_g, ins, sts
+        torch.cuda.empty_cache()
+        B = hi - lo
+        m = self.measure(opname, xs, dy, dS, steps, 2)
+        rec, _ = self.analyse(opname, m, xs, B, T, H, M, N)
+        rec["tokens_per_s"] = GB * T / (m["ms_per_step"] * 1e-3)
+        rec.update({"workload": f"gated_delta_rule fwd+bwd, global B{GB} T{T} H{H} {M}x{N} bf16 I/O, {B} sequences per GPU",
+                    "scaling": "strong", "n_gpus": self.world, "steps": steps, "global_batch": GB,
+                    "sharding": "flex_rnn_b200.shard: contiguous batch rows per rank, no collective"})
+        del m["op"]
+        return rec
+
+
+def run_ours(args, rank, world, local):
+    import torch
+    from flex_rnn_b200 import workloads as W
+    bench = Bench(args, rank, world, local)
+    dev = bench.dev
+    opname, B, T, H, M, N = WORKLOADS[args.op]
+    strong = args.op in STRONG and not args.batch
+    if strong:
+        assert B % world == 0, "the global batch must divide over the GPUs"
+        B //= world
+    big = B * T * H * N * 2 * 3 > 2e9
+    no_e2e = args.no_e2e or big      # the host-buffer leg would pin several GB per buffer set: kept to the headline sizes
+    # each rank draws its own shard of the global batch (seed offset by the rank)
+    xs_host, dy_host, dS_host = W.synthetic(args.op if args.op in W.STEPS else opname, B, T, H, M, N, torch.bfloat16, seed=rank,
+                                            device=dev if big else "cpu")
+    xs = [x.to(dev) for x in xs_host]
+    dy, dS = dy_host.to(dev), dS_host.to(dev)
+    bench.probe_fp32_peak()
+    m = bench.measure(opname, xs, dy, dS, args.steps, args.warmup, sample_clocks=True)
+    rec, extra = bench.analyse(opname, m, xs, B, T, H, M, N)
+    ms_per_step = m["ms_per_step"]
+    value = world * B * T / (ms_per_step * 1e-3)
+
+    e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    if not no_e2e:
+        n_e2e = max(4, min(args.steps, 20))
+        e2e_ms, h2d, d2h = bench.measure_e2e(m["op"], xs_host, dy_host, dS_host, n_e2e)
+        e2e = {"value": world * B * T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms, "steps": n_e2e,
+               # per rank; all ranks copy through the same host at once, so this is what one GPU got of the host path
+               "h2d_gbs_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
+               "host_path_gbs_all_ranks": world * (h2d + d2h) / (e2e_ms * 1e-3) / 1e9}
+
+    fw_ms, bw_ms = m["fw_ms"], m["bw_ms"]
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": workload_text(args.op, B, T, H, M, N),
+                       "io_dtype": "bf16", "math_dtype": "fp32", "global_batch": B * world, "seq_len": T,
+                       "parallelism": f"batch shards x{world}, no collective",
+                       "l2": f"no flush: each step streams {extra['stream_mb']:.0f} MB of inputs, outputs, checkpoints and row sums "
+                             "through HBM (L2 is 126 MB)",
+                       "checkpoint_every": rec["checkpoint_every"], "backward": rec["backward"],
+                       "fw_kernel": rec["fw_kernel"], "bw_kernel": rec["bw_kernel"]},
+            "fw_ms": rec["fw_ms"], "bw_ms": rec["bw_ms"],
+            # spread of the per-step device time (forward + backward events of each timed step), rank 0
+            "step_ms_p20_p50_p80": [round(sorted(f + b for f, b in zip(fw_ms, bw_ms))[int(q * (len(fw_ms) - 1))], 4)
+                                    for q in (0.2, 0.5, 0.8)],
+            "roofline_fraction_step": rec["roofline_fraction_step"],
+            "roofline_fraction_fw": rec["roofline_fraction_fw"],
+            "peak_memory_gib": rec["peak_memory_gib"],
+            "roofline": {"bound": "fp32", "kernel": extra["bw_name"], "achieved": extra["achieved_bw"], "peak": bench.fp32_peak,
+                         "unit": "TFLOP/s", "frac": extra["achieved_bw"] / bench.fp32_peak,
+                         "traffic": extra["traffic_bw"],
+                         "traffic_source": "computed from the plan (inputs, dy, dS_T, saved row sums and fp32 checkpoints read; "
+                                           "gradients and dS0 written)",
+                         "algorithmic_bytes": extra["bytes_bw_alg"],
+                         "peak_source": f"measured in this run by the FMA probe kernel ({bench.sms} SMs); HBM copy peak {bench.hbm} GB/s "
+                                        + ("of measured" if bench.peaks else "of fallback"),
+                         "flops_per_launch": extra["flops_bw"], "k_joint": rec["k_joint"], "k_fwd": rec["k_fwd"],
+                         "hbm_bound_ms": rec["hbm_bound_ms"], "fp32_bound_ms": rec["fp32_bound_ms"]},
+            "e2e": e2e,
+            "gpu_launches": 2 * args.steps,
+            "clocks": m["clocks"],
+        }
+    # release the headline workload before the further records allocate theirs
+    del m, xs, dy, dS
+    torch.cuda.empty_cache()
+
+    if not args.no_extras:
+        n_extra = max(3, min(args.steps, 20))
+        if world == 1:
+            others = {}
+            for name in ("rwkv7", "mamba2", "gated_delta_rule"):
+                if name == args.op:
+                    continue
+                o, b2, t2, h2, m2, n2 = WORKLOADS[name]
+                xs2, dy2, dS2 = W.synthetic(o, b2, t2, h2, m2, n2, torch.bfloat16, seed=0)
+                xs2 = [x.to(dev) for x in xs2]
+                mm = bench.measure(o, xs2, dy2.to(dev), dS2.to(dev), n_extra, 3)
+                r2, _ = bench.analyse(o, mm, xs2, b2, t2, h2, m2, n2)
+                r2["workload"] = workload_text(name, b2, t2, h2, m2, n2)
+                r2["steps"] = n_extra
+                others[name] = r2
+                del mm, xs2, dy2, dS2
+                torch.cuda.empty_cache()
+            line["workloads"] = others
+        if args.op == "delta_rule" and not args.batch:
+            c4 = bench.scaling_c4(max(2, min(args.steps, 5)))
+            torch.cuda.empty_cache()
+            if rank == 0:
+                line["scaling_c4"] = c4
+        if world == 1:
+            line["reference_cuda"] = reference_cuda_record(args.op, n_extra)
+
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            # one cold pass, then the mean of three; the same sample as one step of the reference arm
+            heads = cpu_heads(H, T, 4)
+            cpu_sample(opname, B, T, H, M, N, heads)
+            runs = [cpu_sample(opname, B, T, H, M, N, heads) for _ in range(3)]
+            base = runs[-1][0]
+            mean_dt = sum(dt for _, dt in runs) / len(runs)
+            base["value"] = base["value"] * runs[-1][1] / mean_dt
+            base["sample"] += f"; mean of 3 passes after one cold pass ({mean_dt:.2f} s each)"
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        bench.dist.barrier()
+        bench.dist.destroy_process_group()
 
 
 def main():
@@ -225,6 +646,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the benchmark's 8); smaller = profiling case")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the records beside the headline (other workloads, scaling configuration, reference CUDA)")
     args = ap.parse_args()
     if args.batch:
         for k, w in list(WORKLOADS.items()):
@@ -234,238 +657,15 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.gpus != world:
+        sys.exit(f"bench.py: --gpus {args.gpus} but {world} process(es) were launched; for N > 1 start it with "
+                 f"`python -m torch.distributed.run --nnodes=1 --nproc-per-node {args.gpus} bench.py --gpus {args.gpus} ...`")
     if args.impl == "reference":
         run_reference(args, rank, world)
-        return
-    if args.impl == "reference_cuda":
+    elif args.impl == "reference_cuda":
         run_reference_cuda(args, rank, world, local)
-        return
-
-    import torch
-    import torch.distributed as dist
-    import flex_rnn_b200
-    from flex_rnn_b200 import runtime
-    from flex_rnn_b200 import workloads as W
-
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-
-    opname, B, T, H, M, N = WORKLOADS[args.op]
-    strong = args.op in STRONG and not args.batch
-    if strong:
-        assert B % world == 0, "the global batch must divide over the GPUs"
-        B //= world
-    if B * T * H * N * 2 * 3 > 2e9:
-        args.no_e2e = True          # the host-buffer leg would pin several GB per buffer set: kept to the headline sizes
-    step_fn = W.STEPS[opname]
-    # each rank draws its own shard of the global batch (seed offset by the rank)
-    xs_host, dy_host, dS_host = W.synthetic(opname, B, T, H, M, N, torch.bfloat16, seed=rank)
-    xs = [x.to(dev) for x in xs_host]
-    dy, dS = dy_host.to(dev), dS_host.to(dev)
-    op = flex_rnn_b200.jit(step_fn)
-    leaves = [x.requires_grad_() for x in xs]
-
-    stream = torch.cuda.current_stream(dev)
-    fw_ms, bw_ms = [], []
-
-    def one_step(record):
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
-        if record:
-            ev[0].record(stream)
-        y, ST = op(*leaves)
-        if record:
-            ev[1].record(stream)
-        grads = torch.autograd.grad([y, ST], leaves, [dy, dS])
-        if record:
-            ev[2].record(stream)
-        return ev, grads
-
-    def sync_all():
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize(dev)
-
-    for _ in range(args.warmup):
-        one_step(False)
-    sync_all()
-    assert op.forward_func.kernel_status(dev) == 0, "a kernel reported a timed-out wait"
-
-    # FP32 CUDA-core peak, measured now with the library's FMA-only probe kernel
-    sink = torch.zeros(4, device=dev)
-    probe = []
-    for _ in range(5):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        fl = runtime.fp32_peak_probe(sink.data_ptr(), 20000, stream.cuda_stream)
-        e1.record(stream)
-        torch.cuda.synchronize(dev)
-        probe.append(fl / (e0.elapsed_time(e1) * 1e-3) / 1e12)
-    fp32_peak = max(probe[1:])
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    sync_all()
-    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_start.record(stream)
-    evs = []
-    for _ in range(args.steps):
-        ev, _ = one_step(True)
-        evs.append(ev)
-    t_end.record(stream)
-    sync_all()
-    clocks = sampler.stop() if rank == 0 else None
-    total_ms = t_start.elapsed_time(t_end)
-    for ev in evs:
-        fw_ms.append(ev[0].elapsed_time(ev[1]))
-        bw_ms.append(ev[1].elapsed_time(ev[2]))
-    tms = torch.tensor([total_ms], device=dev)
-    if world > 1:
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    total_ms = float(tms.item())
-    ms_per_step = total_ms / args.steps
-    value = world * B * T / (ms_per_step * 1e-3)
-
-    # end to end through the public API with host buffers (pinned), copies in the timed region
-    if args.no_e2e:
-        pin, pdy, pdS = [], dy_host, dS_host
     else:
-        pin = [x.detach().cpu().pin_memory() for x in xs_host]
-        pdy, pdS = dy_host.pin_memory(), dS_host.pin_memory()
-    out_host = None
-
-    # Three streams, two buffer sets: the host->device copy of step i+1 and the device->host copy of step
-    # i-1 run beside the kernels of step i (all of them inside the timed region).
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    host_in = pin + [pdy, pdS]
-    dev_in = [[] if args.no_e2e else [torch.empty_like(p, device=dev) for p in host_in] for _ in range(2)]
-    dev_out = [None, None]
-    ev_in = [torch.cuda.Event() for _ in range(2)]       # inputs of the slot are on the device
-    ev_used = [torch.cuda.Event() for _ in range(2)]     # the kernels are done with the slot's inputs
-    ev_done = [torch.cuda.Event() for _ in range(2)]     # results of the slot are staged
-    ev_out = [torch.cuda.Event() for _ in range(2)]      # results of the slot have reached the host
-
-    def e2e_step(i):
-        nonlocal out_host
-        k = i & 1
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_used[k])
-            for d_, h_ in zip(dev_in[k], host_in):
-                d_.copy_(h_, non_blocking=True)
-            ev_in[k].record(s_in)
-        stream.wait_event(ev_in[k])
-        stream.wait_event(ev_out[k])
-        d = [t.detach().requires_grad_() for t in dev_in[k][:-2]]
-        y, ST = op(*d)
-        grads = torch.autograd.grad([y, ST], d, [dev_in[k][-2], dev_in[k][-1]])
-        res = [y, ST, *grads]
-        if dev_out[k] is None:
-            dev_out[k] = [torch.empty_like(r) for r in res]
-        if out_host is None:
-            out_host = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
-        for o_, r in zip(dev_out[k], res):
-            o_.copy_(r.detach())
-        ev_used[k].record(stream)
-        ev_done[k].record(stream)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(ev_done[k])
-            for h, o_ in zip(out_host, dev_out[k]):
-                h.copy_(o_, non_blocking=True)
-            ev_out[k].record(s_out)
-
-    n_e2e = 0 if args.no_e2e else max(4, min(args.steps, 20))
-    for i in range(0 if args.no_e2e else 4):
-        e2e_step(i)
-    torch.cuda.synchronize(dev)
-    sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(n_e2e):
-        e2e_step(i)
-    stream.wait_stream(s_out)          # the last results must have reached the host
-    stream.wait_stream(s_in)
-    e1.record(stream)
-    torch.cuda.synchronize(dev)
-    sync_all()
-    e2e_ms = torch.tensor([e0.elapsed_time(e1) / max(1, n_e2e)], device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_ms = float(e2e_ms.item())
-    h2d = 0 if args.no_e2e else sum(p.numel() * p.element_size() for p in host_in)
-    d2h = sum(h.numel() * h.element_size() for h in out_host) if out_host else 0
-
-    if rank == 0:
-        plan = op.forward_func.plan
-        fw_src, bw_src = op.forward_func.sources
-        stream_mb = (bytes_io(xs) * 3 + 2 * B * T * H * M * 2 + plan.nck * B * H * M * N * 4 * 2
-                     + len(plan.aux) * B * T * H * M * 4 * 2) / 1e6
-        k_bw = plan.k_joint - plan.k_fwd
-        elems = B * T * H * M * N
-        bw_avg, fw_avg = statistics.mean(bw_ms), statistics.mean(fw_ms)
-        achieved = elems * k_bw / (bw_avg * 1e-3) / 1e12
-        flops_all = elems * plan.k_joint
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        hbm = peaks.get("hbm_gbs", 6650.0)
-        elt = 2
-        bytes_alg = sum(x.numel() * x.element_size() for x in xs) * 2 + (B * T * H * M * elt) * 2 + 2 * B * H * M * N * elt \
-            + sum(x.numel() * x.element_size() for x in xs[:-1])
-        t_fp32 = flops_all / (fp32_peak * 1e12)
-        t_hbm = bytes_alg / (hbm * 1e9)
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
-            "dtype": "fp32", "data": "synthetic",
-            "config": {"workload": f"{args.op} fwd+bwd, B{B} T{T} H{H} {M}x{N} per GPU, bf16 I/O, fp32 state and math",
-                       "io_dtype": "bf16", "global_batch": B * world, "seq_len": T, "parallelism": f"batch shards x{world}, no collective",
-                       "l2": f"no flush: each step streams {stream_mb:.0f} MB of inputs, outputs, checkpoints and row sums "
-                             "through HBM (L2 is 126 MB)",
-                       "checkpoint_every": plan.D, "backward": "reverse re-step" if plan.reverse else "recompute from slots",
-                       "fw_kernel": {"grid": list(fw_src.grid), "block": fw_src.block, "smem": fw_src.smem_bytes,
-                                     "tile": fw_src.info["tile"][:2], "packed_fp32x2": fw_src.info["packed"]},
-                       "bw_kernel": {"grid": list(bw_src.grid), "block": bw_src.block, "smem": bw_src.smem_bytes,
-                                     "tile": bw_src.info["tile"][:2], "packed_fp32x2": bw_src.info["packed"]}},
-            "fw_ms": fw_avg, "bw_ms": bw_avg,
-            # spread of the per-step device time (forward + backward events of each timed step), rank 0
-            "step_ms_p20_p50_p80": [round(sorted(f + b for f, b in zip(fw_ms, bw_ms))[int(q * (len(fw_ms) - 1))], 4)
-                                    for q in (0.2, 0.5, 0.8)],
-            "roofline_fraction_step": max(t_fp32, t_hbm) / (ms_per_step * 1e-3),
-            "roofline": {"bound": "fp32", "kernel": bw_src.name, "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",
-                         "frac": achieved / fp32_peak,
-                         "traffic": NCU_BW_DRAM_BYTES_PER_BH[args.op] * B * H if args.op in NCU_BW_DRAM_BYTES_PER_BH else None,
-                         "algorithmic_bytes": bytes_io(xs) * 2 + B * T * H * M * 2,
-                         "peak_source": f"measured in this run by the FMA probe kernel ({sms} SMs); HBM copy peak {hbm} GB/s "
-                                        + ("of measured" if peaks else "of fallback"),
-                         "flops_per_launch": elems * k_bw, "k_joint": plan.k_joint, "k_fwd": plan.k_fwd,
-                         "hbm_bound_ms": t_hbm * 1e3, "fp32_bound_ms": t_fp32 * 1e3},
-            "e2e": {"value": (world * B * T / (e2e_ms * 1e-3)) if n_e2e else None, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms},
-            "gpu_launches": 2 * args.steps,
-            "clocks": clocks,
-        }
-        if not args.no_cpu_baseline and world == 1:
-            # one cold pass, then the mean of three (about ten seconds of CPU work on all host threads)
-            heads = H if T <= 1024 else 4          # bounds the autograd graph's memory for long sequences
-            cpu_sample(opname, B, T, H, M, N, heads)
-            runs = [cpu_sample(opname, B, T, H, M, N, heads) for _ in range(3)]
-            base = runs[-1][0]
-            mean_dt = sum(dt for _, dt in runs) / len(runs)
-            base["value"] = base["value"] * runs[-1][1] / mean_dt
-            base["sample"] += f"; mean of 3 passes after one cold pass ({mean_dt:.2f} s each)"
-            line["cpu_baseline"] = base
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        run_ours(args, rank, world, local)
 
 
 if __name__ == "__main__":

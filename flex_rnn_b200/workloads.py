@@ -43,10 +43,14 @@ CONFIGS = {
 }
 
 
-def synthetic(op: str, B: int, T: int, H: int, M: int, N: int, dtype=torch.bfloat16, seed: int = 0):
-    """(inputs + [initial state], d_output [B,T,H,M], d_final_state [B,H,M,N])."""
-    g = torch.Generator().manual_seed(seed)
-    n = lambda *s: torch.randn(*s, generator=g)
+def synthetic(op: str, B: int, T: int, H: int, M: int, N: int, dtype=torch.bfloat16, seed: int = 0, device="cpu"):
+    """(inputs + [initial state], d_output [B,T,H,M], d_final_state [B,H,M,N]).
+
+    Drawn on the CPU generator by default (every device then sees identical
+    values); ``device`` draws on that device's generator instead, for sizes
+    that are too large to draw on the host (the scaling configuration)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    n = lambda *s: torch.randn(*s, generator=g, device=device)
     unit = lambda x: F.normalize(x, dim=-1)
     if op == "delta_rule":
         xs = [unit(n(B, T, H, 1, N)), unit(n(B, T, H, 1, N)), n(B, T, H, M, 1), torch.sigmoid(n(B, T, H, 1, 1)),
@@ -63,7 +67,7 @@ def synthetic(op: str, B: int, T: int, H: int, M: int, N: int, dtype=torch.bfloa
         xs = [q, w, k, v, -kk, kk * torch.sigmoid(n(B, T, H, 1, N)), 0.1 * n(B, H, M, N)]
     elif op == "mamba2":
         xs = [n(B, T, H, M, 1), F.softplus(n(B, T, H, 1, 1) - 1.0), -torch.exp(n(1, 1, H, 1, 1)),
-              n(B, T, H, 1, N) * N ** -0.5, n(B, T, H, 1, N) * N ** -0.5, torch.zeros(B, H, M, N)]
+              n(B, T, H, 1, N) * N ** -0.5, n(B, T, H, 1, N) * N ** -0.5, torch.zeros(B, H, M, N, device=device)]
     else:
         raise KeyError(op)
     dy = n(B, T, H, M)
