@@ -88,6 +88,19 @@ FRNN_DEV bool frnn_mbar_try(u64* bar, u32 parity) {
         : "memory");
     return ok != 0;
 }
+// one arrival on an mbarrier that was initialised with a thread count (release semantics at CTA scope:
+// the arriving thread's earlier shared-memory writes are visible to whoever sees the phase complete)
+FRNN_DEV void frnn_mbar_arrive(u64* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(frnn_smem_addr(bar)) : "memory");
+}
+// Register reallocation between the warpgroups (4 warps) of a CTA: a warpgroup that needs few registers gives
+// some back to the SM's pool, one that needs many takes them.  Executed by all warps of a warpgroup.
+template <int N> FRNN_DEV void frnn_regs_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> FRNN_DEV void frnn_regs_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+// barrier over a subset of the CTA's warps (named barrier `id` in 1..15, `nthreads` a multiple of 32)
+FRNN_DEV void frnn_group_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 FRNN_DEV float frnn_shfl_xor(float v, int off) { return __shfl_xor_sync(0xffffffffu, v, off); }
 FRNN_DEV void frnn_block_sync() { __syncthreads(); }
 FRNN_DEV void frnn_warp_sync() { __syncwarp(); }

@@ -882,6 +882,17 @@ class KernelBuilder:
               f"[{it.base} + (long)({t0} + tl) * {it.stride_t}L + (long)j * {it.inner}L];")
             w.close()
 
+    def emit_plain_direct(self, stage: str, t0: str, nv: str, tidv: str, nthr: int):
+        """Threads ``tidv`` in [0, nthr): copy one chunk of the plainly loaded
+        items from global memory straight into the raw stage buffer."""
+        w = self.w
+        for it in self.plain_items:
+            w.open(f"for (int e = {tidv}; e < ({nv}) * {it.length}; e += {nthr})")
+            w(f"const int tl = e / {it.length}, j = e % {it.length};")
+            w(f"(({CTYPE[it.dt]}*)({stage} + {it.off} + tl * {it.rowb}))[j] = (({'const ' + CTYPE[it.dt]}*){it.ptr})"
+              f"[{it.base} + (long)({t0} + tl) * {it.stride_t}L + (long)j * {it.inner}L];")
+            w.close()
+
     def emit_plain_store(self, stage: str):
         w, t = self.w, self.t
         for k, (it, cnt) in enumerate(self.plain_regs()):
@@ -891,9 +902,11 @@ class KernelBuilder:
             w(f"if (tl < {self.D}) (({CTYPE[it.dt]}*)({stage} + {it.off} + tl * {it.rowb}))[j] = pl{k}[q];")
             w.close()
 
-    def emit_convert(self, raw: str, wk: str, nv: str):
-        """All threads: raw chunk -> fp32 work buffer, evaluating hoisted nodes."""
+    def emit_convert(self, raw: str, wk: str, nv: str, tidv: str = "tid", nthr: Optional[int] = None):
+        """Threads ``tidv`` in [0, nthr) (default: the whole CTA): raw chunk -> fp32
+        work buffer, evaluating hoisted nodes."""
         w, t = self.w, self.t
+        nthr = nthr or t.NT
         hoisted = {n.name: n for n in self.hoisted}
 
         def closure(targets: List[str]) -> List[str]:
@@ -917,7 +930,7 @@ class KernelBuilder:
                 continue
             order = closure(targets)
             vw = 4 if ln % 4 == 0 else (2 if ln % 2 == 0 else 1)   # elements per thread and iteration
-            w.open(f"for (int e = tid; e < {nv} * {ln // vw}; e += {t.NT})")
+            w.open(f"for (int e = {tidv}; e < {nv} * {ln // vw}; e += {nthr})")
             w(f"const int tl = e / {ln // vw}, i = (e % {ln // vw}) * {vw}; (void)i;")
 
             def one(c, cls=cls):
@@ -1038,7 +1051,7 @@ class KernelBuilder:
         w.close()
 
     def emit_obuf_flush(self, obuf: str, nrows: str, vidx: int, nvals: int, dt: int, ptr: str, idx_of_row, stride_m: int,
-                        aligned: bool):
+                        aligned: bool, tidv: str = "tid", nthr: Optional[int] = None):
         """All threads: write ``nrows`` parked timesteps of value slot ``vidx`` to
         global memory with wide stores.  ``idx_of_row(s)`` gives the element
         offset of row m0 at parked row ``s``."""
@@ -1047,7 +1060,7 @@ class KernelBuilder:
         while t.MB % vw:
             vw //= 2
         fast = stride_m == 1 and aligned
-        w.open(f"for (int it = tid; it < ({nrows}) * {t.MB // vw}; it += {t.NT})")
+        w.open(f"for (int it = {tidv}; it < ({nrows}) * {t.MB // vw}; it += {nthr or t.NT})")
         w(f"const int s = it / {t.MB // vw}, mm = (it % {t.MB // vw}) * {vw};")
         w(f"float v[{vw}];")
         cnt = min(4, vw)
@@ -1319,7 +1332,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                   seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
                   step_unroll: int = 2, min_blocks: int = 1, pack2: bool = False,
-                  col_major: bool = False) -> KernelSource:
+                  col_major: bool = False, helper_warps: int = 0) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -1337,6 +1350,15 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     Per-column and per-head gradient partials of ``kflush`` consecutive steps
     are collected in a shared ring and reduced over the row groups together.
 
+    With ``helper_warps`` > 0 the CTA is warp-specialised: the tile's threads
+    (the compute warps) only run the scan - work-buffer reads, arithmetic,
+    shuffles, stores of partials - while the extra warps stage the inputs (TMA
+    issue, conversion of each raw chunk into one of two fp32 work buffers,
+    hoisted nodes) and reduce and store the gradient partials of one half of
+    the ring while the compute warps fill the other.  The two sides meet only
+    on mbarriers (work buffer full / empty, ring half full / empty), every wait
+    time-bounded; the compute warps never wait for a block-wide barrier.
+
     Parameters, in order: used inputs, d_outputs, d_final_states,
     checkpoints, aux, d_initial_states, input gradients, error word.
     """
@@ -1346,6 +1368,24 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     w, t = kb.w, tile
     if t.MB != p.M:
         raise LoweringError("the backward kernel needs all rows of a head in one CTA")
+    ws = helper_warps > 0
+    NCT = t.NT
+    # Register file: the hardware allots registers to a CTA as if its thread count were rounded up to whole
+    # warpgroups (128 threads).  When the compute warps fill whole warpgroups, the helpers are one more warpgroup,
+    # and the two sides rebalance their registers at kernel start (the helpers need few, the scan needs many).
+    regs_launch = regs_compute = regs_helper = 0
+    if ws and NCT % 128 == 0:
+        helper_warps = 4
+        regs_launch = min(248, 65536 // (max(1, min_blocks) * (NCT + 128)) // 8 * 8)
+        regs_helper = min(regs_launch, 56)
+        regs_compute = min(248, (regs_launch + (regs_launch - regs_helper) * 128 // NCT) // 8 * 8)
+    elif ws:
+        helper_warps = 1
+    HT = 32 * helper_warps
+    if ws:
+        ring_bufs = 2
+    if NCT + HT > 1024:
+        raise LoweringError("too many threads for one CTA")
     ns = len(p.states)
     stcls = p.st_cls()
     nin = len(p.inputs)
@@ -1413,27 +1453,33 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     slot_bytes = slot_elems * 4
     ck_tma = (not rev) and use_tma and slot_bytes % 16 == 0
     BAR_BYTES = 128
+    wk_bufs = 2 if ws else 1
+    wk_floats = kb.wk_bytes // 4
     off_stage = BAR_BYTES
     off_wk = off_stage + stage_bytes       # one raw buffer (free again once a chunk is converted)
-    off_slots = off_wk + kb.wk_bytes
+    off_slots = off_wk + wk_bufs * kb.wk_bytes
     off_ring = off_slots + nphys * ns * slot_bytes
     # per-row gradients written every step (dv ...) are parked next to the ring and stored at flush time
     row_st = [go for go in grads if go.cls == M1 and not go.over_t and not go.atomic] if redw else []
     off_ob = off_ring + ring_bytes
     ob_bytes = ring_bufs * kflush * len(row_st) * p.M * 4
     smem_bytes = off_ob + ob_bytes
+    # mbarriers: 0 staged inputs, 2 checkpoint copy; with helper warps 3,4 work buffer full, 5,6 work buffer empty,
+    # 7,8 ring half full, 9,10 ring half empty
+    B_RAW, B_CK, B_WKF, B_WKE, B_RGF, B_RGE = 0, 2, 3, 5, 7, 9
 
     w(_header(prelude))
     mode = f"reverse re-step, resync every {dck} steps" if rev else f"chunk {D} = {nslots} segments x {seg} steps"
     w(f"// backward scan: B={p.B} T={p.T} H={p.H} M={p.M} N={p.N}; tile R={t.R} C={t.C} L={t.L}; {mode}; "
-      f"gradient partials flushed every {kflush} steps")
+      f"gradient partials flushed every {kflush} steps"
+      + (f"; {helper_warps} helper warp(s) stage the inputs and flush the partials" if ws else ""))
     kb.emit_tma_issue("bw_issue")
 
-    w(f'extern "C" __global__ void __launch_bounds__({t.NT}, {min_blocks})')
+    w(f'extern "C" __global__ void __launch_bounds__({NCT + HT}, {min_blocks})')
     w.open(f"{kname}({', '.join(kb.param_decl)})")
     w("FRNN_DYN_SMEM(smem);")
     kb.emit_thread_ids()
-    w("u64* full = (u64*)smem;        // [0],[1]: staged inputs   [2]: checkpoint copy")
+    w("u64* full = (u64*)smem;        // mbarriers")
     w(f"unsigned char* stage = smem + {off_stage};")
     w(f"float* wk = (float*)(smem + {off_wk});")
     if nphys:
@@ -1443,82 +1489,23 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"float* obuf = (float*)(smem + {off_ob}); (void)obuf;")
     has_tma = bool(kb.tma_items)
     w.open("if (tid == 0)")
-    w("frnn_mbar_init(&full[0], 1); frnn_mbar_init(&full[1], 1); frnn_mbar_init(&full[2], 1); frnn_mbar_init_fence();")
+    w(f"frnn_mbar_init(&full[{B_RAW}], 1); frnn_mbar_init(&full[1], 1); frnn_mbar_init(&full[{B_CK}], 1);")
+    if ws:
+        w(f"frnn_mbar_init(&full[{B_WKF}], {HT}); frnn_mbar_init(&full[{B_WKF + 1}], {HT});")
+        w(f"frnn_mbar_init(&full[{B_WKE}], {NCT}); frnn_mbar_init(&full[{B_WKE + 1}], {NCT});")
+        w(f"frnn_mbar_init(&full[{B_RGF}], {NCT}); frnn_mbar_init(&full[{B_RGF + 1}], {NCT});")
+        w(f"frnn_mbar_init(&full[{B_RGE}], {HT}); frnn_mbar_init(&full[{B_RGE + 1}], {HT});")
+    w("frnn_mbar_init_fence();")
     w.close()
     w("frnn_block_sync();")
-    kb.emit_plain_decl()
     tma_call = (", " + kb.tma_issue_call) if has_tma else ""
     ckspec = TensorSpec((p.B, p.H, nck_store, p.M, p.N), _contig((p.B, p.H, nck_store, p.M, p.N)), DT_F32)
-
-    def ck_fetch(kexpr: str, physexpr: str):
-        """Start the copy of checkpoint ``kexpr`` into physical slot ``physexpr``."""
-        if ck_tma:
-            w.open("if (tid == 0)")
-            w("frnn_async_proxy_fence();")
-            w(f"frnn_mbar_expect_tx(&full[2], {ns * slot_bytes}u);")
-            for k in range(ns):
-                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
-                w(f"frnn_bulk_g2s(slots + ((long)({physexpr}) * {ns} + {k}) * {slot_elems}, ck{k} + {base}, {slot_bytes}u, &full[2]);")
-            w.close()
-        else:
-            for k in range(ns):
-                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
-                w(f"for (int e = tid; e < {slot_elems}; e += {t.NT}) "
-                  f"slots[((long)({physexpr}) * {ns} + {k}) * {slot_elems} + e] = ck{k}[{base} + e];")
-
     first_c = nchunk - 1
     nv_first = p.T - first_c * D
-    if kb.plain_items:
-        kb.emit_plain_load(str(first_c * D), str(nv_first))
-        kb.emit_plain_store("stage")
-    if has_tma:
-        w.open("if (warp == 0)")
-        w(f"bw_issue(stage, &full[0], {first_c * D}, {nv_first}, lane, b, h, m0{tma_call});")
-        w.close()
-    if not rev:
-        ck_fetch(str(first_c), "0")
 
-    body = Body(w, t, g_bw2.shape, pack2, col_major)
-    body.shape.update(g_aux2.shape)
-    dshape = (p.B, p.H, p.M, p.N)
-    for k in range(ns):
-        body.declare(dnext_names[k], stcls)
-        dspec = TensorSpec(dshape, _contig(dshape), p.states[k].dt)
-        kb.emit_tile_global(vname(dnext_names[k]), dspec, f"dsT_{k}",
-                            _elem_off(dspec, [(0, "b"), (1, "h")]), 2, 3, load=True)
-        body.declare(p.st_names[k], stcls)
-    for i in const_inputs:
-        kb.emit_const_input(body, p.in_names[i], p.in_cls(i), p.inputs[i], f"in{i}", IN_DIMS)
-    for go in grads:
-        if go.over_t and go.cls == M1:
-            w(f"float gacc{go.index}[{t.R}];")
-            w("#pragma unroll")
-            w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] = 0.0f;")
-        if go.cls == MN:
-            # matrix-per-head inputs are time-invariant: their gradient tile accumulates in registers
-            w(f"float gmat{go.index}[{t.R * t.C}];")
-            w("#pragma unroll")
-            w(f"for (int i = 0; i < {t.R * t.C}; i++) gmat{go.index}[i] = 0.0f;")
-    # time-invariant per-column / per-head gradients: work item (ring row s, element j) always falls to the
-    # same thread and accumulator, which sums it over the row groups and over time; atomics combine at the end
-    tinv = [go for go in pm_vec + pm_sc if go.over_t]
-    ntel = sum(p.N if go.cls == N1 else 1 for go in tinv)
-    nred_per_thread = (kflush * ntel + t.NT - 1) // t.NT if tinv else 0
-
-    def tinv_locate(jexpr: str):
-        """Emit `ro` (offset in a ring row) for compact element index jexpr."""
-        w("int ro = 0;")
-        cum = 0
-        for go in tinv:
-            n_el = p.N if go.cls == N1 else 1
-            w(f"if ({jexpr} >= {cum} && {jexpr} < {cum + n_el}) ro = {ring_off[go.index]} + ({jexpr} - {cum});")
-            cum += n_el
-
-    if tinv:
-        w(f"float racc[{max(1, nred_per_thread)}];")
-        w("#pragma unroll")
-        w(f"for (int q = 0; q < {max(1, nred_per_thread)}; q++) racc[q] = 0.0f;")
-    w("int rcnt = 0, rhalf = 0, rt_first = 0; (void)rcnt; (void)rhalf; (void)rt_first;")
+    def csync(why: str = ""):
+        """Barrier over the compute warps."""
+        w((f"frnn_group_sync(1, {NCT});" if ws else "frnn_block_sync();") + (f"   // {why}" if why else ""))
 
     # element offsets inside one ring row
     ring_off: Dict[int, int] = {}
@@ -1530,26 +1517,65 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         ring_off[go.index] = pos
         pos += 1
 
-    def emit_flush():
-        """Reduce the collected steps over the row groups and write the gradients."""
-        if not redw:
+    # time-invariant per-column / per-head gradients: work item (ring row s, element j) always falls to the
+    # same thread and accumulator, which sums it over the row groups and over time; atomics combine at the end
+    tinv = [go for go in pm_vec + pm_sc if go.over_t]
+    ntel = sum(p.N if go.cls == N1 else 1 for go in tinv)
+    FT = HT if ws else NCT                      # threads that run the flush
+    ftid = "hl" if ws else "tid"
+    nred_per_thread = (kflush * ntel + FT - 1) // FT if tinv else 0
+
+    def tinv_locate(jexpr: str):
+        """Emit `ro` (offset in a ring row) for compact element index jexpr."""
+        w("int ro = 0;")
+        cum = 0
+        for go in tinv:
+            n_el = p.N if go.cls == N1 else 1
+            w(f"if ({jexpr} >= {cum} && {jexpr} < {cum + n_el}) ro = {ring_off[go.index]} + ({jexpr} - {cum});")
+            cum += n_el
+
+    def emit_racc_decl():
+        if tinv:
+            w(f"float racc[{max(1, nred_per_thread)}];")
+            w("#pragma unroll")
+            w(f"for (int q = 0; q < {max(1, nred_per_thread)}; q++) racc[q] = 0.0f;")
+
+    def emit_racc_final():
+        if not tinv:
             return
-        w.open("if (rcnt > 0)")
-        w("frnn_block_sync();   // all partials of this group are in the ring")
-        w(f"const float* rr = ring + rhalf * {kflush * step_floats};")
+        w("#pragma unroll")
+        w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
+        w(f"const int it = {ftid} + q * {FT}, j = it % {ntel};")
+        w.open(f"if (it < {kflush * ntel})")
+        cum = 0
+        for go in tinv:
+            n_el = p.N if go.cls == N1 else 1
+            w.open(f"if (j >= {cum} && j < {cum + n_el})")
+            dims = [(0, "b"), (2, "h")] + ([(4, f"(j - {cum})")] if go.cls == N1 else [])
+            w(f"frnn_atomic_add((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
+            w.close()
+            cum += n_el
+        w.close()
+        w.close()
+
+    def flush_body(half: str, rcnt: str, rt_first: str):
+        """Reduce the ``rcnt`` collected steps of ring half ``half`` over the row groups and write the
+        gradients; run by the threads ``ftid`` in [0, FT)."""
+        w(f"const float* rr = ring + ({half}) * {kflush * step_floats};")
         for vi, go in enumerate(row_st):
-            kb.emit_obuf_flush(f"(obuf + rhalf * {kflush * len(row_st) * p.M})", "rcnt", vi, len(row_st), go.spec.dt,
+            kb.emit_obuf_flush(f"(obuf + ({half}) * {kflush * len(row_st) * p.M})", rcnt, vi, len(row_st), go.spec.dt,
                                f"dx{go.index}",
-                               lambda sx, go=go: _elem_off(go.spec, [(0, "b"), (1, f"rt_first - {sx}"), (2, "h")]),
+                               lambda sx, go=go: _elem_off(go.spec, [(0, "b"), (1, f"({rt_first}) - {sx}"), (2, "h")]),
                                go.spec.st(3),
-                               go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)))
+                               go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)),
+                               tidv=ftid, nthr=FT)
         nq = p.N // vw
         stream_vec = [go for go in pm_vec if not go.over_t]
         if stream_vec:
-            w(f"for (int it = tid; it < rcnt * {len(stream_vec) * nq}; it += {t.NT}) {{")
+            w(f"for (int it = {ftid}; it < ({rcnt}) * {len(stream_vec) * nq}; it += {FT}) {{")
             w.ind += 1
             w(f"const int s = it / {len(stream_vec) * nq}, rem = it % {len(stream_vec) * nq}, vi = rem / {nq}, c0 = (rem % {nq}) * {vw};")
-            w(f"const int tt = rt_first - s; (void)tt;")
+            w(f"const int tt = ({rt_first}) - s; (void)tt;")
             w(f"float a[{vw}];")
             w("#pragma unroll")
             w(f"for (int q = 0; q < {vw}; q++) a[q] = 0.0f;")
@@ -1581,9 +1607,9 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w("}")
         stream_sc = [go for go in pm_sc if not go.over_t]
         if stream_sc:
-            w(f"for (int it = tid; it < rcnt * {len(stream_sc)}; it += {t.NT}) {{")
+            w(f"for (int it = {ftid}; it < ({rcnt}) * {len(stream_sc)}; it += {FT}) {{")
             w.ind += 1
-            w(f"const int s = it / {len(stream_sc)}, si = it % {len(stream_sc)}, tt = rt_first - s; (void)tt;")
+            w(f"const int s = it / {len(stream_sc)}, si = it % {len(stream_sc)}, tt = ({rt_first}) - s; (void)tt;")
             w("int ro = 0;")
             for k, go in enumerate(stream_sc):
                 w(f"if (si == {k}) ro = {ring_off[go.index]};")
@@ -1602,18 +1628,153 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if tinv:
             w("#pragma unroll")
             w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
-            w(f"const int it = tid + q * {t.NT}, s = it / {ntel}, j = it % {ntel};")
-            w.open("if (s < rcnt)")
+            w(f"const int it = {ftid} + q * {FT}, s = it / {ntel}, j = it % {ntel};")
+            w.open(f"if (s < ({rcnt}))")
             tinv_locate("j")
             w("float a = 0.0f;")
             w(f"for (int gi = 0; gi < {t.RG}; gi++) a += rr[s * {step_floats} + gi * {redw_pad} + ro];")
             w("racc[q] += a;")
             w.close()
             w.close()
-        if ring_bufs == 1:
-            w("frnn_block_sync();   // single ring: readers done before the next group is written")
+
+    # ================================================================== helper warps
+    if ws:
+        w.open(f"if (tid >= {NCT})")
+        if regs_launch and regs_helper < regs_launch:
+            w(f"frnn_regs_release<{regs_helper}>();")
+        w(f"const int hl = tid - {NCT}, hlane = hl & 31; (void)hlane;")
+        hbody = Body(w, t, {}, False, False)
+        for i in const_inputs:
+            if p.in_cls(i) == S11:      # time-invariant scalars feed hoisted nodes: the helpers evaluate those
+                kb.emit_const_input(hbody, p.in_names[i], S11, p.inputs[i], f"in{i}", IN_DIMS)
+        hsync = "frnn_warp_sync();" if helper_warps == 1 else f"frnn_group_sync(2, {HT});"
+        emit_racc_decl()
+        w("int hg = 0; (void)hg;   // flush groups served so far")
+
+        def h_issue(t0e: str, nve: str):
+            """Helper: start the copies of one chunk into the raw buffer (it must be free)."""
+            if kb.plain_items:
+                kb.emit_plain_direct("stage", t0e, nve, "hl", HT)
+            if has_tma:
+                w.open("if (hl < 32)")
+                w(f"bw_issue(stage, &full[{B_RAW}], {t0e}, {nve}, hlane, b, h, m0{tma_call});")
+                w.close()
+
+        def h_convert(ce: str, nve: str):
+            """Helper: raw chunk number ``ce`` (in processing order) -> work buffer ce & 1."""
+            if has_tma:
+                w(f"if (!frnn_mbar_wait(&full[{B_RAW}], ({ce}) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+            if kb.plain_items:
+                w(hsync + "   // plain copies of the chunk are visible")
+            w(f"if (({ce}) >= 2 && !frnn_mbar_wait(&full[{B_WKE} + (({ce}) & 1)], ((({ce}) >> 1) - 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+            w(f"float* wkh = wk + (({ce}) & 1) * {wk_floats}; (void)wkh;")
+            kb.emit_convert("stage", "wkh", nve, tidv="hl", nthr=HT)
+            w(f"frnn_mbar_arrive(&full[{B_WKF} + (({ce}) & 1)]);")
+            w(hsync + "   // every helper thread is done reading the raw buffer")
+
+        h_issue(str(first_c * D), str(nv_first))
+        w.open("")
+        h_convert("0", str(nv_first))
+        w.close()
+        if nchunk > 1:
+            h_issue(str((first_c - 1) * D), str(D))
+        w("#pragma unroll 1")
+        w.open(f"for (int c = 0; c < {nchunk}; c++)")
+        w(f"const int kc = {nchunk - 1} - c, t0 = kc * {D}, nv = min({D}, {p.T} - t0);")
+        w.open(f"if (c + 1 < {nchunk})")
+        h_convert("c + 1", str(D))
+        w.open(f"if (c + 2 < {nchunk})")
+        h_issue(f"(kc - 2) * {D}", str(D))
+        w.close()
+        w.close()
+        if redw:
+            w("#pragma unroll 1")
+            w.open(f"for (int g1 = nv; g1 > 0; g1 -= {kflush})")
+            w(f"const int hh = hg & 1, hcnt = min({kflush}, g1), ht = t0 + g1 - 1;")
+            w(f"if (!frnn_mbar_wait(&full[{B_RGF} + hh], (hg >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+            flush_body("hh", "hcnt", "ht")
+            w(f"frnn_mbar_arrive(&full[{B_RGE} + hh]);")
+            w("hg++;")
+            w.close()
+        w.close()   # chunk loop
+        emit_racc_final()
+        w("return;")
+        w.close()   # helper role
+
+    # ================================================================== compute warps
+    if regs_launch and regs_compute > regs_launch:
+        w(f"frnn_regs_acquire<{regs_compute}>();")
+    if not ws:
+        kb.emit_plain_decl()
+
+    def ck_fetch(kexpr: str, physexpr: str):
+        """Start the copy of checkpoint ``kexpr`` into physical slot ``physexpr``."""
+        if ck_tma:
+            w.open("if (tid == 0)")
+            w("frnn_async_proxy_fence();")
+            w(f"frnn_mbar_expect_tx(&full[{B_CK}], {ns * slot_bytes}u);")
+            for k in range(ns):
+                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
+                w(f"frnn_bulk_g2s(slots + ((long)({physexpr}) * {ns} + {k}) * {slot_elems}, ck{k} + {base}, {slot_bytes}u, &full[{B_CK}]);")
+            w.close()
         else:
-            w("rhalf ^= 1;")
+            for k in range(ns):
+                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
+                w(f"for (int e = tid; e < {slot_elems}; e += {NCT}) "
+                  f"slots[((long)({physexpr}) * {ns} + {k}) * {slot_elems} + e] = ck{k}[{base} + e];")
+
+    if not ws:
+        if kb.plain_items:
+            kb.emit_plain_load(str(first_c * D), str(nv_first))
+            kb.emit_plain_store("stage")
+        if has_tma:
+            w.open("if (warp == 0)")
+            w(f"bw_issue(stage, &full[{B_RAW}], {first_c * D}, {nv_first}, lane, b, h, m0{tma_call});")
+            w.close()
+    if not rev:
+        ck_fetch(str(first_c), "0")
+
+    body = Body(w, t, g_bw2.shape, pack2, col_major)
+    body.shape.update(g_aux2.shape)
+    dshape = (p.B, p.H, p.M, p.N)
+    for k in range(ns):
+        body.declare(dnext_names[k], stcls)
+        dspec = TensorSpec(dshape, _contig(dshape), p.states[k].dt)
+        kb.emit_tile_global(vname(dnext_names[k]), dspec, f"dsT_{k}",
+                            _elem_off(dspec, [(0, "b"), (1, "h")]), 2, 3, load=True)
+        body.declare(p.st_names[k], stcls)
+    for i in const_inputs:
+        kb.emit_const_input(body, p.in_names[i], p.in_cls(i), p.inputs[i], f"in{i}", IN_DIMS)
+    for go in grads:
+        if go.over_t and go.cls == M1:
+            w(f"float gacc{go.index}[{t.R}];")
+            w("#pragma unroll")
+            w(f"for (int r = 0; r < {t.R}; r++) gacc{go.index}[r] = 0.0f;")
+        if go.cls == MN:
+            # matrix-per-head inputs are time-invariant: their gradient tile accumulates in registers
+            w(f"float gmat{go.index}[{t.R * t.C}];")
+            w("#pragma unroll")
+            w(f"for (int i = 0; i < {t.R * t.C}; i++) gmat{go.index}[i] = 0.0f;")
+    if not ws:
+        emit_racc_decl()
+    w("int rcnt = 0, rhalf = 0, rt_first = 0, gidx = 0; (void)rcnt; (void)rhalf; (void)rt_first; (void)gidx;")
+
+    def emit_flush():
+        """The collected steps are complete: reduce them over the row groups and write the gradients
+        (or, with helper warps, hand the ring half over to them)."""
+        if not redw:
+            return
+        w.open("if (rcnt > 0)")
+        if ws:
+            w(f"frnn_mbar_arrive(&full[{B_RGF} + rhalf]);   // this thread's partials of the group are in the ring")
+            w("gidx++; rhalf ^= 1;")
+        else:
+            w("frnn_block_sync();   // all partials of this group are in the ring")
+            flush_body("rhalf", "rcnt", "rt_first")
+            if ring_bufs == 1:
+                w("frnn_block_sync();   // single ring: readers done before the next group is written")
+            else:
+                w("rhalf ^= 1;")
         w("rcnt = 0;")
         w.close()
 
@@ -1640,7 +1801,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     def emit_restep(tlexpr: str):
         w.open("")
         w(f"const int tl = {tlexpr};")
-        w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
+        w(f"const float* wkt = wkc + tl * {kb.wk_row}; (void)wkt;")
         sub = body.child()
         read_wk_inputs(sub, g_aux2)
         sub.graph(g_aux2)
@@ -1700,6 +1861,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 emit_unstep()
             sub.graph(g_bw2, allow_over_m=True)
         outs = g_bw2.outputs
+        if redw:
+            w.open("if (rcnt == 0)")
+            w("rt_first = t;")
+            if ws:
+                w(f"if (gidx >= 2 && !frnn_mbar_wait(&full[{B_RGE} + rhalf], ((gidx >> 1) - 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+            w.close()
         for go in grads:
             if go.cls != M1:
                 continue
@@ -1726,7 +1893,6 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 raise LoweringError("matrix gradient came out as a sum over rows")
             sub.loops(MN, lambda r, c, go=go: f"gmat{go.index}[{r}*{t.C}+{c}] += {sub.at(go.value, r, c)};")
         if redw:
-            w("if (rcnt == 0) rt_first = t;")
             w(f"float* rb = ring + (rhalf * {kflush} + rcnt) * {step_floats} + rg * {redw_pad};")
             for go in pm_vec:
                 val = go.value
@@ -1756,22 +1922,27 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     w("#pragma unroll 1")
     w.open(f"for (int c = 0; c < {nchunk}; c++)")
     w(f"const int kc = {nchunk - 1} - c, t0 = kc * {D}, nv = min({D}, {p.T} - t0);")
-    w("unsigned char* sp = stage;")
-    if kb.plain_items:
-        w("if (kc > 0) {")
-        w.ind += 1
-        kb.emit_plain_load(f"(t0 - {D})", str(D))
-        w.ind -= 1
-        w("}")
-    if has_tma:
-        w(f"if (!frnn_mbar_wait(&full[0], c & 1, err, {ERR_STAGE_TIMEOUT})) return;")
-    w("frnn_block_sync();   // previous chunk's work buffer is no longer read; plain stores are visible")
-    kb.emit_convert("sp", "wk", "nv")
-    w("frnn_block_sync();   // work buffer complete; the raw buffer may be refilled")
-    if has_tma:
-        w.open("if (warp == 0 && kc >= 1)")
-        w(f"bw_issue(sp, &full[0], (kc - 1) * {D}, {D}, lane, b, h, m0{tma_call});")
-        w.close()
+    if ws:
+        w(f"if (!frnn_mbar_wait(&full[{B_WKF} + (c & 1)], (c >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+        w(f"const float* wkc = wk + (c & 1) * {wk_floats}; (void)wkc;")
+    else:
+        w("unsigned char* sp = stage;")
+        if kb.plain_items:
+            w("if (kc > 0) {")
+            w.ind += 1
+            kb.emit_plain_load(f"(t0 - {D})", str(D))
+            w.ind -= 1
+            w("}")
+        if has_tma:
+            w(f"if (!frnn_mbar_wait(&full[{B_RAW}], c & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+        w("frnn_block_sync();   // previous chunk's work buffer is no longer read; plain stores are visible")
+        kb.emit_convert("sp", "wk", "nv")
+        w("frnn_block_sync();   // work buffer complete; the raw buffer may be refilled")
+        if has_tma:
+            w.open("if (warp == 0 && kc >= 1)")
+            w(f"bw_issue(sp, &full[{B_RAW}], (kc - 1) * {D}, {D}, lane, b, h, m0{tma_call});")
+            w.close()
+        w("const float* wkc = wk; (void)wkc;")
 
     if rev:
         # reload an exact forward state at the end of this chunk when it is a checkpoint boundary
@@ -1788,7 +1959,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"#pragma unroll {step_unroll}")
         w.open("for (int tl = g1 - 1; tl >= g0; tl--)")
         w("const int t = t0 + tl; (void)t;")
-        w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
+        w(f"const float* wkt = wkc + tl * {kb.wk_row}; (void)wkt;")
         w.open("")
         emit_bw_step()
         w.close()
@@ -1799,7 +1970,9 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"const int par = c & 1, nseg = (nv + {seg - 1}) / {seg};")
         w(f"#define PHYS(j) (par ? ({nphys - 1} - (j)) : (j))")
         if ck_tma:
-            w(f"if (!frnn_mbar_wait(&full[2], c & 1, err, {ERR_CKPT_TIMEOUT})) return;")
+            w(f"if (!frnn_mbar_wait(&full[{B_CK}], c & 1, err, {ERR_CKPT_TIMEOUT})) return;")
+        elif ws:
+            csync("the plainly copied checkpoint is complete")
         # phase A: rebuild the segment bases
         slot_rw("PHYS(0)", store=False)
         w("#pragma unroll 1")
@@ -1824,7 +1997,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.close()
         w.open("")
         w(f"const int tl = j * {seg} + i, t = t0 + tl; (void)t;")
-        w(f"const float* wkt = wk + tl * {kb.wk_row}; (void)wkt;")
+        w(f"const float* wkt = wkc + tl * {kb.wk_row}; (void)wkt;")
         emit_bw_step()
         w.close()
         if redw and kflush > 1:
@@ -1838,14 +2011,16 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.close()   # i loop
         w.close()   # if j < nseg
         w.open(f"if (j == {nphys - 1} && kc > 0)")
-        w("frnn_block_sync();   // every thread is done with the slot that is overwritten next")
+        csync("every thread is done with the slot that is overwritten next")
         ck_fetch("kc - 1", f"PHYS({nphys - 1})")
         w.close()
         w.close()   # j loop
         if redw and kflush > 1:
             emit_flush()
         w("#undef PHYS")
-    if kb.plain_items:
+    if ws:
+        w(f"frnn_mbar_arrive(&full[{B_WKE} + (c & 1)]);   // this thread no longer reads the chunk's work buffer")
+    elif kb.plain_items:
         w("if (kc > 0) {")
         w.ind += 1
         kb.emit_plain_store("stage")
@@ -1863,25 +2038,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if go.cls == MN:
             kb.emit_tile_global(f"gmat{go.index}", go.spec, f"dx{go.index}", _elem_off(go.spec, [(0, "b"), (2, "h")]),
                                 3, 4, load=False, add=True)
-    if tinv:
-        w("#pragma unroll")
-        w.open(f"for (int q = 0; q < {nred_per_thread}; q++)")
-        w(f"const int it = tid + q * {t.NT}, j = it % {ntel};")
-        w.open(f"if (it < {kflush * ntel})")
-        cum = 0
-        for go in tinv:
-            n_el = p.N if go.cls == N1 else 1
-            w.open(f"if (j >= {cum} && j < {cum + n_el})")
-            dims = [(0, "b"), (2, "h")] + ([(4, f"(j - {cum})")] if go.cls == N1 else [])
-            w(f"frnn_atomic_add((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
-            w.close()
-            cum += n_el
-        w.close()
-        w.close()
+    if not ws:
+        emit_racc_final()
     w.close()
-    return KernelSource(kname, w.text(), (1, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
+    return KernelSource(kname, w.text(), (1, p.H, p.B), NCT + HT, smem_bytes, kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
                          "reverse": rev, "hoisted": [n.name for n in kb.hoisted], "tile": [t.R, t.C, t.MB],
-                         "packed": bool(pack2)}, kb.tmaps)
+                         "packed": bool(pack2), "helper_warps": helper_warps}, kb.tmaps)

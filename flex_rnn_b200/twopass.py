@@ -88,7 +88,10 @@ class Tuning:
     kflush: int = 8          # steps of gradient partials reduced together (lowered until shared memory fits)
     reverse: int = 1         # use the reverse re-step when the state update is additive
     rev_stage: int = 16      # reverse mode: timesteps per staged chunk
-    rev_resync: int = 4      # reverse mode: chunks between exact checkpoints
+    rev_resync: int = 4      # reverse mode: chunks between exact checkpoints (without helper warps)
+    rev_ckpt: int = 64       # reverse mode with helper warps: timesteps between exact checkpoints
+    bw_helper: int = 1       # backward helper warps: they stage the inputs and flush the gradient partials while the
+                             # tile's warps run the scan; 0 = every warp does everything, with block barriers between
     fw_unroll: int = 4       # unroll factor of the timestep loops
     bw_unroll: int = 4
     slot_search: int = 1     # generic backward: try 4 slots x 2 steps before seg x nslots
@@ -334,35 +337,56 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         # a (b,h) state small enough for a CTA of four warps leaves room for a second CTA on the SM
         # (Mamba-2 64x128: 7 % faster backward than one CTA of eight warps)
         tu.bw_min_blocks = 2 if bw_tile.NT <= 128 and B * H * (M // bw_tile.MB) > n_sm else 1
-    if reverse is not None:
-        pairs = [(sg, tu.nslots) for sg in range(tu.rev_stage, 0, -1)]
-    else:
+
+    def flush_options(helper: int):
+        out, k = [], max(1, tu.kflush)
+        while k >= 1:
+            out += [(k, 2)] if helper else [(k, 2), (k, 1)]
+            k //= 2
+        return out
+
+    def fits(sg, nsl, kflush, bufs, helper):
+        ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
+                           tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse, helper_warps=helper,
+                           min_blocks=max(1, tu.bw_min_blocks))
+        return ks.smem_bytes <= _bw_smem_limit(tu)
+
+    def fit():
+        """((steps per segment or staged chunk, flush group, ring buffers), slots, helper warps) that fit
+        shared memory, preferring helper warps as long as they do not cost recomputation."""
+        helpers = [1, 0] if tu.bw_helper else [0]
+        if reverse is not None:
+            for helper in helpers:
+                # with helper warps a chunk boundary is cheap: prefer a long flush group over a long staged chunk
+                stages = [s for s in (16, 8, 4) if s <= tu.rev_stage] if helper else list(range(tu.rev_stage, 0, -1))
+                order = [(sg, fl) for fl in flush_options(helper) for sg in stages] if helper else \
+                        [(sg, fl) for sg in stages for fl in flush_options(helper)]
+                for sg, (kflush, bufs) in order:
+                    if fits(sg, tu.nslots, kflush, bufs, helper):
+                        return (sg, kflush, bufs), tu.nslots, helper
+            return None, tu.nslots, 0
         # (steps per segment, slots): fewer recomputed steps first, then what the tuning asks for
         pairs = ([(2, 4)] if tu.slot_search and T >= 8 else []) + [(sg, tu.nslots) for sg in range(tu.seg, 0, -1)]
         if tu.nslots > 1:
             pairs += [(sg, 1) for sg in range(tu.seg, 0, -1)]
-    while choice is None:
-        ks = None
         for sg, nsl in pairs:
-            k = max(1, tu.kflush)
-            cands = []
-            while k >= 1:
-                cands += [(k, 2), (k, 1)]
-                k //= 2
-            for kflush, bufs in cands:
-                ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
-                                   tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse)
-                if ks.smem_bytes <= _bw_smem_limit(tu):
-                    choice = (sg, kflush, bufs)
-                    tu.nslots = nsl
-                    break
-            if choice or ks is None:
-                break
-        if choice is None and auto_blocks and tu.bw_min_blocks > 1:
+            for helper in helpers:
+                for kflush, bufs in flush_options(helper):
+                    if fits(sg, nsl, kflush, bufs, helper):
+                        return (sg, kflush, bufs), nsl, helper
+        return None, tu.nslots, 0
+
+    while choice is None:
+        choice, nsl, helper = fit()
+        if choice is not None:
+            tu.bw_helper, tu.nslots = helper, nsl
+            break
+        if auto_blocks and tu.bw_min_blocks > 1:
             tu.bw_min_blocks = 1          # half an SM's shared memory is not enough: one CTA per SM after all
             continue
         break
-    seg0 = pairs[0][0]
+    if reverse is not None and choice is not None and tu.bw_helper:
+        reverse.resync = max(1, tu.rev_ckpt // choice[0])
     if choice is None:
         raise lower.LoweringError(f"the backward kernel of a {M}x{N} state does not fit shared memory")
     if reverse is not None:
@@ -462,7 +486,8 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
         bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
                            plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
                            kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
-                           min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major))
+                           min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major),
+                           helper_warps=tu.bw_helper)
         if bw.smem_bytes <= _bw_smem_limit(tu):
             return bw
     return None

@@ -38,6 +38,7 @@ struct emu_cta {
     int nthreads;
     std::barrier<>* block_bar;
     std::vector<std::barrier<>*> warp_bar;
+    std::barrier<>* group_bar[16] = {nullptr};   // named barriers, created on first use with that use's thread count
     std::vector<float> xchg;          // [nthreads]
     unsigned char* smem;
     std::mutex mtx;
@@ -65,19 +66,29 @@ FRNN_DEV u64 frnn_now_ns() {
     return (u64)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
-// mbarrier emulation inside the 8 bytes: [phase:16 | arrived:16 | pending:32 (signed)]
-struct emu_mbar { int pending; unsigned short arrived; unsigned short phase; };
+// mbarrier emulation inside the 8 bytes: pending transaction bytes (signed), arrivals still expected in this phase,
+// the arrival count the barrier was initialised with (15 bits) and the phase parity (1 bit)
+struct emu_mbar { int pending; unsigned short remaining; unsigned short count_phase; };
 static_assert(sizeof(emu_mbar) == 8, "mbarrier emulation must fit the 64-bit word");
 FRNN_DEV void emu_mbar_settle(emu_mbar* b) {
-    if (b->arrived && b->pending == 0) { b->phase++; b->arrived = 0; }
+    if (b->remaining == 0 && b->pending == 0) { b->count_phase ^= 1u; b->remaining = (unsigned short)(b->count_phase >> 1); }
 }
-FRNN_DEV void frnn_mbar_init(u64* bar, u32) { emu_mbar* b = (emu_mbar*)bar; b->pending = 0; b->arrived = 0; b->phase = 0; }
+FRNN_DEV void frnn_mbar_init(u64* bar, u32 count) {
+    emu_mbar* b = (emu_mbar*)bar; b->pending = 0; b->remaining = (unsigned short)count; b->count_phase = (unsigned short)(count << 1);
+}
 FRNN_DEV void frnn_mbar_init_fence() {}
 FRNN_DEV void frnn_async_proxy_fence() {}
 FRNN_DEV void frnn_mbar_expect_tx(u64* bar, u32 bytes) {
     std::lock_guard<std::mutex> g(emu_ctx->mtx);
     emu_mbar* b = (emu_mbar*)bar;
-    b->pending += (int)bytes; b->arrived = 1; emu_mbar_settle(b);
+    if (b->remaining == 0) { fprintf(stderr, "emu: more arrivals on an mbarrier than it was initialised for\n"); abort(); }
+    b->pending += (int)bytes; b->remaining--; emu_mbar_settle(b);
+}
+FRNN_DEV void frnn_mbar_arrive(u64* bar) {
+    std::lock_guard<std::mutex> g(emu_ctx->mtx);
+    emu_mbar* b = (emu_mbar*)bar;
+    if (b->remaining == 0) { fprintf(stderr, "emu: more arrivals on an mbarrier than it was initialised for\n"); abort(); }
+    b->remaining--; emu_mbar_settle(b);
 }
 FRNN_DEV void frnn_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
     if (((uintptr_t)dst & 15) || ((uintptr_t)src & 15) || (bytes & 15)) {
@@ -117,7 +128,7 @@ FRNN_DEV void frnn_tma_load_4d(void* dst, const frnn_tmap* m, int c0, int c1, in
 FRNN_DEV bool frnn_mbar_try(u64* bar, u32 parity) {
     std::lock_guard<std::mutex> g(emu_ctx->mtx);
     emu_mbar* b = (emu_mbar*)bar;
-    bool ok = ((b->phase & 1u) != parity);
+    bool ok = ((b->count_phase & 1u) != parity);
     if (!ok) std::this_thread::yield();
     return ok;
 }
@@ -130,7 +141,18 @@ FRNN_DEV float frnn_shfl_xor(float v, int off) {
     c->warp_bar[w]->arrive_and_wait();
     return r;
 }
+template <int N> FRNN_DEV void frnn_regs_release() {}
+template <int N> FRNN_DEV void frnn_regs_acquire() {}
 FRNN_DEV void frnn_block_sync() { emu_ctx->block_bar->arrive_and_wait(); }
+FRNN_DEV void frnn_group_sync(int id, int nthreads) {
+    emu_cta* c = emu_ctx;
+    {
+        std::lock_guard<std::mutex> g(c->mtx);
+        if (id < 1 || id > 15 || nthreads % 32) { fprintf(stderr, "emu: bad named barrier %d/%d\n", id, nthreads); abort(); }
+        if (!c->group_bar[id]) c->group_bar[id] = new std::barrier<>((std::ptrdiff_t)nthreads);
+    }
+    c->group_bar[id]->arrive_and_wait();
+}
 FRNN_DEV void frnn_warp_sync() { emu_ctx->warp_bar[threadIdx.x >> 5]->arrive_and_wait(); }
 FRNN_DEV void frnn_atomic_add(float* p, float v) { std::lock_guard<std::mutex> g(emu_atomic_mtx); *p += v; }
 FRNN_DEV void frnn_report(int* err, int code) { std::lock_guard<std::mutex> g(emu_atomic_mtx); if (*err == 0) *err = code; }
@@ -173,6 +195,7 @@ static void emu_launch(emu_entry_t fn, const unsigned grid[3], unsigned nthreads
                     });
                 for (auto& t : th) t.join();
                 for (auto* b : wb) delete b;
+                for (auto*& gb : cta.group_bar) { delete gb; gb = nullptr; }
                 free(raw);
             }
 }
