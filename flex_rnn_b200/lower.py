@@ -261,8 +261,10 @@ def op_expr(n: Node, a: List[str]) -> str:
 class Body:
     """Emits per-thread code for graph nodes over R x C register tiles."""
 
-    def __init__(self, w: W, tile: Tile, shapes: Dict[str, Shape], pack2: bool = False, col_major: bool = False):
+    def __init__(self, w: W, tile: Tile, shapes: Dict[str, Shape], pack2: bool = False, col_major: bool = False,
+                 max_acc: int = 4):
         self.w = w
+        self.max_acc = max(1, max_acc)   # independent accumulators per kept element of a sum
         self.t = tile
         self.shape = dict(shapes)
         self.pack2 = pack2            # packed fp32x2 arithmetic for column-varying values
@@ -281,7 +283,7 @@ class Body:
 
     def child(self) -> "Body":
         """A body for a nested scope: sees this body's values, keeps the same options."""
-        return Body(self.w, self.t, self.shape, self.pack2, self.col_major)
+        return Body(self.w, self.t, self.shape, self.pack2, self.col_major, self.max_acc)
 
     def varies_c(self, a) -> bool:
         return isinstance(a, str) and bool(self.shape[a][1])
@@ -470,7 +472,7 @@ class Body:
             red_c = n.over_n and ss[1]
             kept = self.size(n.shape)
             chain = (t.R if red_r else 1) * (t.C if red_c else 1)
-            nacc = max(1, min(4, chain // 4))
+            nacc = max(1, min(4, self.max_acc, chain // 4))
             while kept * nacc > 32 and nacc > 1:
                 nacc //= 2
             w.open("")
@@ -567,7 +569,7 @@ class Body:
         else:
             kept = t.C // 2
             chain = t.R
-        nacc = max(1, min(2 if red_c else 4, chain // 4))
+        nacc = max(1, min(2 if red_c else 4, self.max_acc, chain // 4))
         while kept * nacc > 16 and nacc > 1:
             nacc //= 2
         w.open("")
@@ -1136,7 +1138,7 @@ def _stage_inputs(kb: KernelBuilder, p: Problem, used: Sequence[bool], allow_mn:
 def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, tile: Tile,
                  dstage: int, dck: int, use_tma: bool, min_blocks: int, prelude: str,
                  kname: str = "frnn_fw", final_ckpt: bool = False, step_unroll: int = 2, pack2: bool = False,
-                 col_major: bool = False) -> KernelSource:
+                 col_major: bool = False, max_acc: int = 2) -> KernelSource:
     """Forward scan.  ``g`` computes [*outputs, *new_states, *aux] from
     [*inputs, *states].  Kernel parameters, in order: used inputs, initial
     states, outputs, final states, checkpoints, aux, error word.  With
@@ -1203,7 +1205,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
         w(f"fw_issue(stage, &full[0], 0, min({dstage}, {p.T}), lane, b, h, m0{tma_call});")
         w.close()
 
-    body = Body(w, t, g2.shape, pack2, col_major)
+    body = Body(w, t, g2.shape, pack2, col_major, max_acc)
     ckspec = TensorSpec((p.B, p.H, nck_store, p.M, p.N), _contig((p.B, p.H, nck_store, p.M, p.N)), DT_F32)
     for k in range(ns):
         body.declare(p.st_names[k], stcls)
@@ -1332,7 +1334,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                   seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
                   step_unroll: int = 2, min_blocks: int = 1, pack2: bool = False,
-                  col_major: bool = False, helper_warps: int = 0) -> KernelSource:
+                  col_major: bool = False, helper_warps: int = 0, max_acc: int = 1) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -1734,7 +1736,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     if not rev:
         ck_fetch(str(first_c), "0")
 
-    body = Body(w, t, g_bw2.shape, pack2, col_major)
+    body = Body(w, t, g_bw2.shape, pack2, col_major, max_acc)
     body.shape.update(g_aux2.shape)
     dshape = (p.B, p.H, p.M, p.N)
     for k in range(ns):
