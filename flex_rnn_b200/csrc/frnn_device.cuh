@@ -117,7 +117,74 @@ FRNN_DEV frnn_pk frnn_mul2(frnn_pk a, frnn_pk b) { return __fmul2_rn(a, b); }
 FRNN_DEV frnn_pk frnn_add2(frnn_pk a, frnn_pk b) { return __fadd2_rn(a, b); }
 FRNN_DEV float frnn_rcpf(float x) { return __frcp_rn(x); }
 FRNN_DEV float frnn_divf(float a, float b) { return __fdividef(a, b); }
+// ---- Tensor Memory as on-chip scratch ----------------------------------------------------------
+// sm_100 has 256 KB of Tensor Memory per SM (128 lanes x 512 columns of 32 bits) beside the register file and
+// shared memory.  It is meant for tensor-core accumulators, but tcgen05.st / tcgen05.ld move plain 32-bit
+// registers in and out, so a kernel that never touches the tensor cores can park register tiles there.  Warp w
+// of a CTA reaches lanes 32*(w%4) .. 32*(w%4)+31; thread i of the warp owns lane 32*(w%4)+i, and each access
+// moves N consecutive columns of that lane.  An address is (lane << 16) | column.
+// Allocation (whole CTA, by one warp, a power of two >= 32 columns) blocks while the SM has no room, so a kernel
+// must free what it holds on every path out.
+FRNN_DEV void frnn_tmem_alloc(u32* base_out_smem, u32 ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(frnn_smem_addr(base_out_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+FRNN_DEV void frnn_tmem_dealloc(u32 taddr, u32 ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+FRNN_DEV void frnn_tmem_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+FRNN_DEV void frnn_tmem_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+FRNN_DEV void frnn_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+FRNN_DEV void frnn_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+FRNN_DEV u32 frnn_tmem_lane_base(int warp) { return ((u32)(warp & 3) * 32u) << 16; }
+FRNN_DEV int frnn_smem_add(int* p, int v) { return atomicAdd(p, v); }
+FRNN_DEV void frnn_tmem_st1(u32 taddr, const float* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "f"(v[0]) : "memory");
+}
+FRNN_DEV void frnn_tmem_ld1(u32 taddr, float* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=f"(v[0]) : "r"(taddr) : "memory");
+}
+FRNN_DEV void frnn_tmem_st2(u32 taddr, const float* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "f"(v[0]), "f"(v[1]) : "memory");
+}
+FRNN_DEV void frnn_tmem_ld2(u32 taddr, float* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(taddr) : "memory");
+}
+FRNN_DEV void frnn_tmem_st4(u32 taddr, const float* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+}
+FRNN_DEV void frnn_tmem_ld4(u32 taddr, float* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(taddr) : "memory");
+}
+FRNN_DEV void frnn_tmem_st8(u32 taddr, const float* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+FRNN_DEV void frnn_tmem_ld8(u32 taddr, float* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "r"(taddr) : "memory");
+}
+FRNN_DEV void frnn_tmem_st16(u32 taddr, const float* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]), "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]) : "memory");
+}
+FRNN_DEV void frnn_tmem_ld16(u32 taddr, float* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]) : "r"(taddr) : "memory");
+}
 #endif  // !FRNN_EMU
+
+// N registers of one thread to / from N consecutive Tensor Memory columns of its lane, in power-of-two pieces
+template <int N> FRNN_DEV void frnn_tmem_st(u32 taddr, const float* v) {
+    if constexpr (N >= 16) { frnn_tmem_st16(taddr, v); frnn_tmem_st<N - 16>(taddr + 16, v + 16); }
+    else if constexpr (N >= 8) { frnn_tmem_st8(taddr, v); frnn_tmem_st<N - 8>(taddr + 8, v + 8); }
+    else if constexpr (N >= 4) { frnn_tmem_st4(taddr, v); frnn_tmem_st<N - 4>(taddr + 4, v + 4); }
+    else if constexpr (N >= 2) { frnn_tmem_st2(taddr, v); frnn_tmem_st<N - 2>(taddr + 2, v + 2); }
+    else if constexpr (N == 1) { frnn_tmem_st1(taddr, v); }
+}
+template <int N> FRNN_DEV void frnn_tmem_ld(u32 taddr, float* v) {
+    if constexpr (N >= 16) { frnn_tmem_ld16(taddr, v); frnn_tmem_ld<N - 16>(taddr + 16, v + 16); }
+    else if constexpr (N >= 8) { frnn_tmem_ld8(taddr, v); frnn_tmem_ld<N - 8>(taddr + 8, v + 8); }
+    else if constexpr (N >= 4) { frnn_tmem_ld4(taddr, v); frnn_tmem_ld<N - 4>(taddr + 4, v + 4); }
+    else if constexpr (N >= 2) { frnn_tmem_ld2(taddr, v); frnn_tmem_ld<N - 2>(taddr + 2, v + 2); }
+    else if constexpr (N == 1) { frnn_tmem_ld1(taddr, v); }
+}
 
 #ifndef FRNN_WAIT_LIMIT_NS
 #define FRNN_WAIT_LIMIT_NS 2000000000ull

@@ -1334,7 +1334,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                   seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
                   step_unroll: int = 2, min_blocks: int = 1, pack2: bool = False,
-                  col_major: bool = False, helper_warps: int = 0, max_acc: int = 1) -> KernelSource:
+                  col_major: bool = False, helper_warps: int = 0, max_acc: int = 1,
+                  tmem_slots: int = 0) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -1360,6 +1361,16 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     the ring while the compute warps fill the other.  The two sides meet only
     on mbarriers (work buffer full / empty, ring half full / empty), every wait
     time-bounded; the compute warps never wait for a block-wide barrier.
+
+    With ``tmem_slots`` = nslots > 0 (generic mode, helper warps on) the segment
+    bases live in Tensor Memory instead of shared memory: each thread parks its
+    register tile in its own lane (tcgen05.st) and fetches it back (tcgen05.ld),
+    so four bases of a 128x128 state fit on the SM beside one shared-memory
+    landing slot for the checkpoint copy, and a chunk of 8 steps costs 10
+    re-steps instead of 16.  The CTA allocates the columns at start and frees
+    them on every path out (the scan runs inside a function object; after it
+    returns, normally or on a timed-out wait, each warp checks in and the
+    allocating warp frees the columns).
 
     Parameters, in order: used inputs, d_outputs, d_final_states,
     checkpoints, aux, d_initial_states, input gradients, error word.
@@ -1450,7 +1461,17 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     redw_pad = (redw + 3) // 4 * 4
     step_floats = t.RG * redw_pad
     ring_bytes = ring_bufs * kflush * step_floats * 4 if redw else 0
-    nphys = 0 if rev else max(nslots, 2)
+    tm = (not rev) and ws and tmem_slots > 0
+    if tm and tmem_slots != nslots:
+        raise LoweringError("the Tensor Memory slots must be the segment slots")
+    nphys = 0 if rev else (1 if tm else max(nslots, 2))
+    tile_regs = t.R * t.C
+    tm_slot_cols = ((NCT + 127) // 128) * ns * tile_regs          # columns of one slot: a tile per state and warpgroup
+    tm_cols = 32
+    while tm and tm_cols < nslots * tm_slot_cols:
+        tm_cols *= 2
+    if tm and tm_cols > 512 // max(1, min_blocks):
+        raise LoweringError("the segment bases do not fit the Tensor Memory of one SM")
     slot_elems = p.M * p.N
     slot_bytes = slot_elems * 4
     ck_tma = (not rev) and use_tma and slot_bytes % 16 == 0
@@ -1497,9 +1518,20 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"frnn_mbar_init(&full[{B_WKE}], {NCT}); frnn_mbar_init(&full[{B_WKE + 1}], {NCT});")
         w(f"frnn_mbar_init(&full[{B_RGF}], {NCT}); frnn_mbar_init(&full[{B_RGF + 1}], {NCT});")
         w(f"frnn_mbar_init(&full[{B_RGE}], {HT}); frnn_mbar_init(&full[{B_RGE + 1}], {HT});")
+    if tm:
+        w("((int*)&full[13])[0] = 0;      // warps that are done with Tensor Memory")
     w("frnn_mbar_init_fence();")
     w.close()
+    if tm:
+        w.open("if (warp == 0)")
+        w(f"frnn_tmem_alloc((u32*)&full[12], {tm_cols}u);")
+        w("frnn_tmem_fence_before_sync();")
+        w.close()
     w("frnn_block_sync();")
+    if tm:
+        w("frnn_tmem_fence_after_sync();")
+        w("const u32 tm_base = *(volatile u32*)&full[12];")
+        w(f"const u32 tm_mine = tm_base + frnn_tmem_lane_base(warp) + (u32)(warp >> 2) * {ns * tile_regs}u;   // this thread's lane, this warpgroup's columns")
     tma_call = (", " + kb.tma_issue_call) if has_tma else ""
     ckspec = TensorSpec((p.B, p.H, nck_store, p.M, p.N), _contig((p.B, p.H, nck_store, p.M, p.N)), DT_F32)
     first_c = nchunk - 1
@@ -1706,6 +1738,9 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     # ================================================================== compute warps
     if regs_launch and regs_compute > regs_launch:
         w(f"frnn_regs_acquire<{regs_compute}>();")
+    if tm:
+        w("auto scan = [&]() -> void {")
+        w.ind += 1
     if not ws:
         kb.emit_plain_decl()
 
@@ -1779,6 +1814,14 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 w("rhalf ^= 1;")
         w("rcnt = 0;")
         w.close()
+
+    def tmem_rw(jexpr: str, store: bool):
+        """Register tiles of all states <-> Tensor Memory slot ``jexpr``."""
+        for k in range(ns):
+            fn = "frnn_tmem_st" if store else "frnn_tmem_ld"
+            w(f"{fn}<{tile_regs}>(tm_mine + (u32)({jexpr}) * {tm_slot_cols}u + {k * tile_regs}u, {vname(p.st_names[k])});")
+        if not store:
+            w("frnn_tmem_wait_ld();")
 
     def slot_rw(physexpr: str, store: bool):
         for k in range(ns):
@@ -1969,30 +2012,45 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         emit_flush()
         w.close()
     else:
-        w(f"const int par = c & 1, nseg = (nv + {seg - 1}) / {seg};")
+        w(f"const int par = c & 1, nseg = (nv + {seg - 1}) / {seg}; (void)par;")
         w(f"#define PHYS(j) (par ? ({nphys - 1} - (j)) : (j))")
         if ck_tma:
             w(f"if (!frnn_mbar_wait(&full[{B_CK}], c & 1, err, {ERR_CKPT_TIMEOUT})) return;")
         elif ws:
             csync("the plainly copied checkpoint is complete")
         # phase A: rebuild the segment bases
-        slot_rw("PHYS(0)", store=False)
+        slot_rw("0" if tm else "PHYS(0)", store=False)
+        if tm:
+            # the landing slot is free as soon as every thread holds its tile: fetch the next checkpoint a chunk ahead
+            csync("every thread has read the landing slot")
+            w.open("if (kc > 0)")
+            ck_fetch("kc - 1", "0")
+            w.close()
+            tmem_rw("0", store=True)
         w("#pragma unroll 1")
         w.open("for (int j = 1; j < nseg; j++)")
         w("#pragma unroll 1")
         w.open(f"for (int i = 0; i < {seg}; i++)")
         emit_restep(f"(j - 1) * {seg} + i")
         w.close()
-        slot_rw("PHYS(j)", store=True)
+        if tm:
+            tmem_rw("j", store=True)
+        else:
+            slot_rw("PHYS(j)", store=True)
         w.close()
+        if tm:
+            w("frnn_tmem_wait_st();")
         # phase B: walk the chunk backwards
         w("#pragma unroll 1")
-        w.open(f"for (int j = {nphys - 1}; j >= 0; j--)")
+        w.open(f"for (int j = {(nslots if tm else nphys) - 1}; j >= 0; j--)")
         w.open("if (j < nseg)")
         w(f"const int seglen = min({seg}, nv - j * {seg});")
         w("#pragma unroll 1")
         w.open("for (int i = seglen - 1; i >= 0; i--)")
-        slot_rw("PHYS(j)", store=False)
+        if tm:
+            tmem_rw("j", store=False)
+        else:
+            slot_rw("PHYS(j)", store=False)
         w("#pragma unroll 1")
         w.open("for (int i2 = 0; i2 < i; i2++)")
         emit_restep(f"j * {seg} + i2")
@@ -2012,10 +2070,11 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             emit_flush()
         w.close()   # i loop
         w.close()   # if j < nseg
-        w.open(f"if (j == {nphys - 1} && kc > 0)")
-        csync("every thread is done with the slot that is overwritten next")
-        ck_fetch("kc - 1", f"PHYS({nphys - 1})")
-        w.close()
+        if not tm:
+            w.open(f"if (j == {nphys - 1} && kc > 0)")
+            csync("every thread is done with the slot that is overwritten next")
+            ck_fetch("kc - 1", f"PHYS({nphys - 1})")
+            w.close()
         w.close()   # j loop
         if redw and kflush > 1:
             emit_flush()
@@ -2042,10 +2101,23 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                                 3, 4, load=False, add=True)
     if not ws:
         emit_racc_final()
+    if tm:
+        w.ind -= 1
+        w("};")
+        w("scan();")
+        w("// out of the scan, normally or after a timed-out wait: check in, and the allocating warp frees Tensor Memory")
+        w("frnn_warp_sync();")
+        w("if (lane == 0) frnn_smem_add((int*)&full[13], 1);")
+        w.open("if (warp == 0)")
+        w("const u64 t_exit = frnn_now_ns();")
+        w(f"while (frnn_smem_add((int*)&full[13], 0) < {NCT // 32} && frnn_now_ns() - t_exit < 2 * FRNN_WAIT_LIMIT_NS) {{}}")
+        w(f"frnn_tmem_dealloc(tm_base, {tm_cols}u);")
+        w.close()
     w.close()
     return KernelSource(kname, w.text(), (1, p.H, p.B), NCT + HT, smem_bytes, kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
                          "reverse": rev, "hoisted": [n.name for n in kb.hoisted], "tile": [t.R, t.C, t.MB],
-                         "packed": bool(pack2), "helper_warps": helper_warps}, kb.tmaps)
+                         "packed": bool(pack2), "helper_warps": helper_warps, "tmem_cols": tm_cols if tm else 0,
+                         "seg": seg, "nslots": nslots}, kb.tmaps)

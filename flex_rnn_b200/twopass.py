@@ -103,6 +103,9 @@ class Tuning:
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     fw_variant: int = -1     # >= 0: use this member of forward_variants(plan) untimed (tests, reproducible runs)
     bw_variant: int = -1     # >= 0: use this member of backward_variants(plan) untimed
+    bw_tmem: int = 1         # generic backward: keep the segment bases in Tensor Memory when they fit (more slots than
+                             # shared memory holds, hence fewer recomputed steps); needs helper warps
+    bw_tmem_slots: int = 0   # set by the planner: slots kept in Tensor Memory (0 = shared-memory slots)
     fw_acc: int = 2          # independent accumulators per kept element of a sum, forward kernel (measured: 2 is 3-6 %
                              # faster than 4 or 1 on the forward, 1 is 3 % faster than 2 or 4 on the backward)
     bw_acc: int = 1          # the same, backward kernel
@@ -348,16 +351,29 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             k //= 2
         return out
 
-    def fits(sg, nsl, kflush, bufs, helper):
-        ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
-                           tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse, helper_warps=helper,
-                           min_blocks=max(1, tu.bw_min_blocks))
+    def fits(sg, nsl, kflush, bufs, helper, tmem=0):
+        try:
+            ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
+                               tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse, helper_warps=helper,
+                               min_blocks=max(1, tu.bw_min_blocks), tmem_slots=tmem)
+        except lower.LoweringError:
+            if tmem:
+                return False
+            raise
         return ks.smem_bytes <= _bw_smem_limit(tu)
 
     def fit():
         """((steps per segment or staged chunk, flush group, ring buffers), slots, helper warps) that fit
         shared memory, preferring helper warps as long as they do not cost recomputation."""
         helpers = [1, 0] if tu.bw_helper else [0]
+        tu.bw_tmem_slots = 0
+        if reverse is None and tu.bw_helper and tu.bw_tmem and T >= 8:
+            # segment bases in Tensor Memory: as many slots as fit, one step fewer to recompute per slot more
+            for nsl in (8, 4):
+                for kflush, bufs in flush_options(1):
+                    if fits(8 // nsl, nsl, kflush, bufs, 1, tmem=nsl):
+                        tu.bw_tmem_slots = nsl
+                        return (8 // nsl, kflush, bufs), nsl, 1
         if reverse is not None:
             for helper in helpers:
                 # with helper warps a chunk boundary is cheap: prefer a long flush group over a long staged chunk
@@ -491,7 +507,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
                            plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
                            kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
                            min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major),
-                           helper_warps=tu.bw_helper, max_acc=tu.bw_acc)
+                           helper_warps=tu.bw_helper, max_acc=tu.bw_acc, tmem_slots=tu.bw_tmem_slots)
         if bw.smem_bytes <= _bw_smem_limit(tu):
             return bw
     return None

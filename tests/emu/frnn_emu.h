@@ -6,6 +6,8 @@
 // nothing in the library imports or runs this.
 #pragma once
 #define FRNN_EMU 1
+// one OS thread per CUDA thread on a few cores is slow: a bounded device wait must not expire just for that
+#define FRNN_WAIT_LIMIT_NS 240000000000ull
 #include <atomic>
 #include <barrier>
 #include <chrono>
@@ -40,6 +42,8 @@ struct emu_cta {
     std::vector<std::barrier<>*> warp_bar;
     std::barrier<>* group_bar[16] = {nullptr};   // named barriers, created on first use with that use's thread count
     std::vector<float> xchg;          // [nthreads]
+    std::vector<float> tmem;          // Tensor Memory: 128 lanes x 512 columns (allocated on first use)
+    int tmem_cols = 0;                // columns the CTA has allocated (0: none)
     unsigned char* smem;
     std::mutex mtx;
 };
@@ -141,6 +145,42 @@ FRNN_DEV float frnn_shfl_xor(float v, int off) {
     c->warp_bar[w]->arrive_and_wait();
     return r;
 }
+// Tensor Memory emulation: one allocation per CTA starting at column 0; aborts on what the hardware forbids
+FRNN_DEV void frnn_tmem_alloc(u32* base_out, u32 ncols) {
+    if ((threadIdx.x & 31) != 0) { emu_ctx->warp_bar[threadIdx.x >> 5]->arrive_and_wait(); return; }
+    {
+        std::lock_guard<std::mutex> g(emu_ctx->mtx);
+        if (ncols < 32 || ncols > 512 || (ncols & (ncols - 1)) || emu_ctx->tmem_cols) { fprintf(stderr, "emu: bad Tensor Memory allocation of %u columns\n", ncols); abort(); }
+        emu_ctx->tmem.assign(128 * 512, -12345.0f);
+        emu_ctx->tmem_cols = (int)ncols;
+        *base_out = 0;
+    }
+    emu_ctx->warp_bar[threadIdx.x >> 5]->arrive_and_wait();
+}
+FRNN_DEV void frnn_tmem_dealloc(u32 taddr, u32 ncols) {
+    if ((threadIdx.x & 31) != 0) return;
+    std::lock_guard<std::mutex> g(emu_ctx->mtx);
+    if (taddr != 0 || (int)ncols != emu_ctx->tmem_cols) { fprintf(stderr, "emu: Tensor Memory freed with the wrong address or size\n"); abort(); }
+    emu_ctx->tmem_cols = 0;
+}
+FRNN_DEV void frnn_tmem_fence_before_sync() {}
+FRNN_DEV void frnn_tmem_fence_after_sync() {}
+FRNN_DEV void frnn_tmem_wait_st() {}
+FRNN_DEV void frnn_tmem_wait_ld() {}
+FRNN_DEV u32 frnn_tmem_lane_base(int warp) { return ((u32)(warp & 3) * 32u) << 16; }
+FRNN_DEV float* emu_tmem_at(u32 taddr, int n) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const u32 lane0 = taddr >> 16, col = taddr & 0xffffu;
+    if (lane0 != (u32)(warp & 3) * 32u || (int)col + n > emu_ctx->tmem_cols) {
+        fprintf(stderr, "emu: Tensor Memory access outside the warp's lanes or the allocation (lane %u col %u n %d)\n", lane0, col, n); abort();
+    }
+    return &emu_ctx->tmem[(size_t)(lane0 + lane) * 512 + col];
+}
+#define EMU_TMEM_FN(N) \
+    FRNN_DEV void frnn_tmem_st##N(u32 taddr, const float* v) { memcpy(emu_tmem_at(taddr, N), v, 4 * N); } \
+    FRNN_DEV void frnn_tmem_ld##N(u32 taddr, float* v) { memcpy(v, emu_tmem_at(taddr, N), 4 * N); }
+EMU_TMEM_FN(1) EMU_TMEM_FN(2) EMU_TMEM_FN(4) EMU_TMEM_FN(8) EMU_TMEM_FN(16)
+FRNN_DEV int frnn_smem_add(int* p, int v) { std::lock_guard<std::mutex> g(emu_atomic_mtx); int o = *p; *p = o + v; return o; }
 template <int N> FRNN_DEV void frnn_regs_release() {}
 template <int N> FRNN_DEV void frnn_regs_acquire() {}
 FRNN_DEV void frnn_block_sync() { emu_ctx->block_bar->arrive_and_wait(); }
