@@ -338,6 +338,26 @@ class Bench:
         self.fp32_peak = max(probe[1:])
         return self.fp32_peak
 
+    def probe_fma_kinds(self):
+        """Share of the measured FP32 peak that register-only loops of the scan kernels' kinds of FMA reach (the
+        library's probe kernels: all operands distinct registers, one operand kept, the Delta Rule step mixes)."""
+        from flex_rnn_b200 import runtime
+        torch = self.torch
+        sink = torch.zeros(4, device=self.dev)
+        src = torch.rand(4096, device=self.dev) * 1e-3
+        out = {}
+        for kind, name in runtime.MIX_PROBES.items():
+            best = 0.0
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.stream)
+                fl = runtime.fp32_mix_probe(kind, sink.data_ptr(), src.data_ptr(), 2000, self.stream.cuda_stream)
+                e1.record(self.stream)
+                torch.cuda.synchronize(self.dev)
+                best = max(best, fl / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+            out[name] = round(best / self.fp32_peak, 4)
+        return out
+
     # ---- one workload, inputs resident in HBM -------------------------------------------------------------
     def measure(self, opname, xs, dy, dS, steps, warmup, sample_clocks=False):
         """Forward + backward of ``jit(step)`` on device-resident arguments: ``warmup`` untimed steps (the first
@@ -428,7 +448,12 @@ class Bench:
         if kref and kref != plan.k_joint:
             rec["roofline_fraction_step_reference_tracer_k"] = elems * kref / (peak * 1e12) / step_s
             rec["k_joint_reference_tracer"] = kref
-        extra = {"bytes_fw_alg": bytes_fw_alg, "bytes_bw_alg": bytes_bw_alg, "traffic_bw": traffic_bw, "traffic_fw": traffic_fw,
+        units = B * H * (M // bw_src.info["tile"][2])
+        per_wave = self.sms * max(1, plan.tuning.bw_min_blocks)
+        issued = (plan.k_joint - plan.k_fwd) / 2 + (plan.n_st if plan.reverse else 0)
+        extra = {"counted_per_issued": ((plan.k_joint - plan.k_fwd) / 2) / issued if plan.reverse else None,
+                 "sm_fill": units / (-(-units // per_wave) * per_wave),
+                 "bytes_fw_alg": bytes_fw_alg, "bytes_bw_alg": bytes_bw_alg, "traffic_bw": traffic_bw, "traffic_fw": traffic_fw,
                  "achieved_bw": elems * k_bw / (bw_avg * 1e-3) / 1e12, "flops_bw": elems * k_bw, "bw_name": bw_src.name,
                  "stream_mb": (traffic_fw + traffic_bw) / 1e6}
         return rec, extra
@@ -539,6 +564,7 @@ def run_ours(args, rank, world, local):
     xs = [x.to(dev) for x in xs_host]
     dy, dS = dy_host.to(dev), dS_host.to(dev)
     bench.probe_fp32_peak()
+    fma_kinds = bench.probe_fma_kinds() if rank == 0 else {}
     m = bench.measure(opname, xs, dy, dS, args.steps, args.warmup, sample_clocks=True)
     rec, extra = bench.analyse(opname, m, xs, B, T, H, M, N)
     ms_per_step = m["ms_per_step"]
@@ -584,7 +610,15 @@ def run_ours(args, rank, world, local):
                          "peak_source": f"measured in this run by the FMA probe kernel ({bench.sms} SMs); HBM copy peak {bench.hbm} GB/s "
                                         + ("of measured" if bench.peaks else "of fallback"),
                          "flops_per_launch": extra["flops_bw"], "k_joint": rec["k_joint"], "k_fwd": rec["k_fwd"],
-                         "hbm_bound_ms": rec["hbm_bound_ms"], "fp32_bound_ms": rec["fp32_bound_ms"]},
+                         "hbm_bound_ms": rec["hbm_bound_ms"], "fp32_bound_ms": rec["fp32_bound_ms"],
+                         # what bounds `frac` below 1: the share of the FP32 peak that FMAs of the kernels' kinds reach in
+                         # register-only loops (probe kernels of the library, measured now), the FMAs the kernel issues per
+                         # counted one, and how evenly the (b,h) recurrences fill the SMs
+                         "fp32_pipe_share_by_fma_kind": fma_kinds,
+                         "counted_per_issued_fma": extra["counted_per_issued"],
+                         "sm_fill": extra["sm_fill"],
+                         "ceiling_frac": (fma_kinds.get("delta_rule_backward_mix_packed", 1.0) * extra["counted_per_issued"]
+                                          * extra["sm_fill"]) if (args.op == "delta_rule" and fma_kinds) else None},
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
             "clocks": m["clocks"],

@@ -27,6 +27,9 @@ _N_PACKED_AUX = 1   # all saved row sums travel in one tensor so the op schema i
 
 
 def _signature(args) -> Tuple:
+    if any(isinstance(s, th.SymInt) for a in args for s in tuple(a.shape) + tuple(a.stride())):
+        raise RuntimeError("flex_rnn_b200 kernels are specialised for concrete shapes and strides; symbolic sizes are not "
+                           "supported (under torch.compile use dynamic=False or mark the sizes static)")
     dev = args[0].device
     return tuple((tuple(a.shape), tuple(s if n > 1 else 0 for s, n in zip(a.stride(), a.shape)), a.dtype) for a in args) + \
         ((dev.type, dev.index),)

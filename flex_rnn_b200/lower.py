@@ -1395,8 +1395,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     elif ws:
         helper_warps = 1
     HT = 32 * helper_warps
-    if ws:
-        ring_bufs = 2
+    ring_bufs = max(1, min(2, ring_bufs))
     if NCT + HT > 1024:
         raise LoweringError("too many threads for one CTA")
     ns = len(p.states)
@@ -1724,8 +1723,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if redw:
             w("#pragma unroll 1")
             w.open(f"for (int g1 = nv; g1 > 0; g1 -= {kflush})")
-            w(f"const int hh = hg & 1, hcnt = min({kflush}, g1), ht = t0 + g1 - 1;")
-            w(f"if (!frnn_mbar_wait(&full[{B_RGF} + hh], (hg >> 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+            w(f"const int hh = hg % {ring_bufs}, hcnt = min({kflush}, g1), ht = t0 + g1 - 1;")
+            w(f"if (!frnn_mbar_wait(&full[{B_RGF} + hh], (hg / {ring_bufs}) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
             flush_body("hh", "hcnt", "ht")
             w(f"frnn_mbar_arrive(&full[{B_RGE} + hh]);")
             w("hg++;")
@@ -1804,7 +1803,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w.open("if (rcnt > 0)")
         if ws:
             w(f"frnn_mbar_arrive(&full[{B_RGF} + rhalf]);   // this thread's partials of the group are in the ring")
-            w("gidx++; rhalf ^= 1;")
+            w(f"gidx++; rhalf = gidx % {ring_bufs};")
         else:
             w("frnn_block_sync();   // all partials of this group are in the ring")
             flush_body("rhalf", "rcnt", "rt_first")
@@ -1910,7 +1909,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w.open("if (rcnt == 0)")
             w("rt_first = t;")
             if ws:
-                w(f"if (gidx >= 2 && !frnn_mbar_wait(&full[{B_RGE} + rhalf], ((gidx >> 1) - 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
+                w(f"if (gidx >= {ring_bufs} && !frnn_mbar_wait(&full[{B_RGE} + rhalf], ((gidx / {ring_bufs}) - 1) & 1, err, {ERR_STAGE_TIMEOUT})) return;")
             w.close()
         for go in grads:
             if go.cls != M1:

@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(HERE, "libfrnn_b200.so")
 SYMBOLS = ["frnn_abi_version", "frnn_last_error", "frnn_compile", "frnn_free", "frnn_module_load",
            "frnn_module_unload", "frnn_launch", "frnn_kernel_attrs", "frnn_l2_flush", "frnn_fp32_peak_probe",
            "frnn_launch_static_scratch", "frnn_static_scratch_capacity", "frnn_tensor_map_encode",
-           "frnn_nvrtc_version", "frnn_status", "frnn_status_post", "frnn_status_check"]
+           "frnn_nvrtc_version", "frnn_status", "frnn_status_post", "frnn_status_check", "frnn_fp32_mix_probe"]
 
 
 class FrnnError(RuntimeError):
@@ -64,6 +64,7 @@ def lib() -> ctypes.CDLL:
         L.frnn_status_check.argtypes = [vp, vp, vp]
         L.frnn_l2_flush.argtypes = [vp, sz, vp]
         L.frnn_fp32_peak_probe.argtypes = [vp, ci, vp, ctypes.POINTER(ctypes.c_double)]
+        L.frnn_fp32_mix_probe.argtypes = [ci, vp, vp, ci, vp, ctypes.POINTER(ctypes.c_double)]
         _lib = L
     return _lib
 
@@ -228,6 +229,17 @@ def status_check(host_word_ptr: int, err_word_ptr: int, stream: int):
 
 def l2_flush(buf_ptr: int, nbytes: int, stream: int):
     _check(lib().frnn_l2_flush(ctypes.c_void_p(buf_ptr), nbytes, ctypes.c_void_p(stream)), "frnn_l2_flush")
+
+
+MIX_PROBES = {0: "ffma_three_distinct_operands", 1: "ffma_one_operand_kept", 2: "ffma2_three_distinct_pairs",
+              3: "ffma2_one_pair_kept", 4: "delta_rule_backward_mix_packed", 5: "delta_rule_forward_mix_scalar"}
+
+
+def fp32_mix_probe(kind: int, sink_ptr: int, in_ptr: int, iters: int, stream: int) -> float:
+    fl = ctypes.c_double()
+    _check(lib().frnn_fp32_mix_probe(int(kind), ctypes.c_void_p(sink_ptr), ctypes.c_void_p(in_ptr), iters,
+                                     ctypes.c_void_p(stream), ctypes.byref(fl)), "frnn_fp32_mix_probe")
+    return fl.value
 
 
 def fp32_peak_probe(sink_ptr: int, iters: int, stream: int) -> float:

@@ -345,11 +345,14 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         tu.bw_min_blocks = 2 if bw_tile.NT <= 128 and B * H * (M // bw_tile.MB) > n_sm else 1
 
     def flush_options(helper: int):
-        out, k = [], max(1, tu.kflush)
+        ks, k = [], max(1, tu.kflush)
         while k >= 1:
-            out += [(k, 2)] if helper else [(k, 2), (k, 1)]
+            ks.append(k)
             k //= 2
-        return out
+        if helper:
+            # a second ring half lets the compute warps go on while the helpers flush: worth more than a longer group
+            return [(k, 2) for k in ks] + [(k, 1) for k in ks]
+        return [(k, b) for k in ks for b in (2, 1)]
 
     def fits(sg, nsl, kflush, bufs, helper, tmem=0):
         try:

@@ -180,6 +180,21 @@ int frnn_l2_flush(void* buf, size_t bytes, void* stream);
  * bounds the recurrent kernels.  `sink` is a device buffer of >= 4 bytes. */
 int frnn_fp32_peak_probe(float* sink, int iters, void* stream, double* flops);
 
+/*
+ * Register-only probe loops of the kinds of FMA the scan kernels execute, one block of 256 threads per SM, timed
+ * by the caller like frnn_fp32_peak_probe; *flops receives the operations performed.  `in` is a device buffer of
+ * at least 512 floats (small finite values), `sink` one of >= 4 bytes.
+ *   kind 0  scalar FFMA, three distinct register operands per instruction
+ *   kind 1  scalar FFMA, one operand kept from the previous instruction
+ *   kind 2  packed FFMA2, three distinct register pairs
+ *   kind 3  packed FFMA2, one pair kept
+ *   kind 4  the Delta Rule backward step's seven FMAs per state element (8x8 register tiles, packed)
+ *   kind 5  the Delta Rule forward step's three FMAs per state element (4x32 register tile, scalar)
+ * The ratio to the peak probe is the share of the FP32 pipe that arithmetic of that kind can reach on this GPU
+ * with this compiler; the benchmark reports it beside the kernels' roofline fraction.
+ */
+int frnn_fp32_mix_probe(int kind, float* sink, const float* in, int iters, void* stream, double* flops);
+
 #ifdef __cplusplus
 }
 #endif

@@ -191,7 +191,10 @@ def test_reference_frontend_on_this_backend_gpu(op_name):
     xs, _, _ = O.make_case(op_name, 2, 9, 2, 16, 16, torch.float32)
     xs = [x.to("cuda:0") for x in xs]
     op2 = ref_jit.jit(O.STEPS[op_name])
-    compiled = torch.compile(lambda *z: op2(*z), fullgraph=True)
+    torch._dynamo.reset()
+    # static shapes: the kernels are specialised for them (recompiling one code location for other shapes
+    # would otherwise switch Dynamo to symbolic sizes)
+    compiled = torch.compile(lambda *z: op2(*z), fullgraph=True, dynamic=False)
     y0, S0 = op(*xs)
     y1, S1 = compiled(*xs)
     assert torch.equal(y0, y1) and torch.equal(S0, S1)
