@@ -272,6 +272,7 @@ class Body:
         self.partial: Dict[str, bool] = {}     # value is a per-row-group partial sum
         self.alias: Dict[str, str] = {}        # value name -> name of the register tile that holds it
         self.fused: Dict[str, Node] = {}       # products folded into the packed FMA of their only consumer
+        self.predeclared: set = set()          # values whose register arrays are declared in an enclosing scope
 
     # -- packed fp32x2 arithmetic (sm_100 `fma.rn.f32x2`) ---------------------------------------
     # Values that vary along the columns are processed two columns at a time: one packed instruction
@@ -403,7 +404,8 @@ class Body:
 
     def declare(self, name: str, s: Shape):
         self.shape[name] = s
-        self.w(f"float {vname(name)}[{self.size(s)}];")
+        if name not in self.predeclared:
+            self.w(f"float {vname(name)}[{self.size(s)}];")
 
     def loops(self, s: Shape, body):
         w = self.w
@@ -1329,13 +1331,27 @@ class Reverse:
     resync: int               # chunks between reloads of an exact forward checkpoint
 
 
+def can_split_post(g_re: StepGraph, g_bw: StepGraph, st_names: Sequence[str]) -> bool:
+    """Whether the backward step can read the post-step state as an input instead of recomputing it: no node may
+    need both a value derived from the post-step state and the pre-step state."""
+    ns_names = list(g_re.outputs)
+    if any(n in g_bw.inputs for n in ns_names):
+        return False
+    probe = g_bw.pruned(g_bw.outputs, g_bw.name, leaves=ns_names)
+    if not all(n in probe.inputs for n in ns_names):
+        return False                      # the backward does not use the post-step state at all
+    dep_next = probe.depends_on(ns_names) - set(ns_names)
+    dep_cur = probe.depends_on(st_names)
+    return not (dep_next & dep_cur) and not (set(ns_names) & dep_cur)
+
+
 def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[str], n_out: int,
                   grads: List[GradOut], dy_names: List[str], dnext_names: List[str], tile: Tile,
                   seg: int, nslots: int, use_tma: bool, prelude: str, kname: str = "frnn_bw",
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
                   step_unroll: int = 2, min_blocks: int = 1, pack2: bool = False,
                   col_major: bool = False, helper_warps: int = 0, max_acc: int = 1,
-                  tmem_slots: int = 0) -> KernelSource:
+                  tmem_slots: int = 0, post_split: bool = False) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -1361,6 +1377,16 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     the ring while the compute warps fill the other.  The two sides meet only
     on mbarriers (work buffer full / empty, ring half full / empty), every wait
     time-bounded; the compute warps never wait for a block-wide barrier.
+
+    With ``post_split`` (generic mode, when ``can_split_post`` holds) the step
+    is evaluated in two parts, as in the reverse mode: the part that needs only
+    the post-step state S_{t+1} runs while the state registers still hold it -
+    they do, from the step handled just before - and the part that needs the
+    pre-step state S_t after S_t has been fetched; the post-step state is then
+    never recomputed inside the backward step.  The first part of step t-1 is
+    issued right after the second part of step t (for the last step of a chunk:
+    at the start of the chunk, before its segment bases are rebuilt), and the
+    forward stores one more fp32 checkpoint, the final state.
 
     With ``tmem_slots`` = nslots > 0 (generic mode, helper warps on) the segment
     bases live in Tensor Memory instead of shared memory: each thread parks its
@@ -1412,6 +1438,14 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if not (dep_next & dep_cur) and not (set(ns_names) & dep_cur) and all(n in probe.inputs for n in ns_names):
             g_bw = probe
             alias_next = ns_names
+    split = False
+    if (not rev) and post_split:
+        if not can_split_post(g_re, g_bw, p.st_names):
+            raise LoweringError("this step's backward cannot be split at the post-step state")
+        ns_names = list(g_re.outputs)
+        g_bw = g_bw.pruned(g_bw.outputs, g_bw.name, leaves=[n for n in ns_names if n not in g_bw.inputs])
+        alias_next = ns_names
+        split = True
     graphs = [g_bw] + ([reverse.graph] if rev else [g_re])
     used_lists = [g.used_inputs() for g in graphs]
     used = [any(u[i] for u in used_lists) for i in range(nin)]
@@ -1420,7 +1454,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     nchunk = (p.T + D - 1) // D
     dck = D * (reverse.resync if rev else 1)
     nck = (p.T + dck - 1) // dck
-    nck_store = nck + (1 if rev else 0)
+    nck_store = nck + (1 if (rev or split) else 0)
 
     for i in range(nin):
         if used[i]:
@@ -1879,31 +1913,92 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                           f"{body.at(st, r, c)} = {body.at(st, r, c)} {sgn} {sub.at(u.args[1], r, c)};")
         w.close()
 
+    step_parts: Dict[str, object] = {}
+
+    def step_body() -> Body:
+        """The Body both parts of the backward step are emitted with (made once: which products are folded
+        into which consumer must not change between two emissions of a part)."""
+        if "sub" not in step_parts:
+            sub = body.child()
+            phase1: List[Node] = []
+            phase2: List[Node] = list(g_bw2.nodes)
+            if alias_next:
+                # part 1 (state registers hold S_{t+1}): every node that does not need S_t
+                for k, nm in enumerate(alias_next):
+                    sub.alias[nm] = p.st_names[k]
+                    sub.shape[nm] = stcls
+                dep_cur = g_bw2.depends_on(p.st_names)
+                if split:
+                    # only what reads the post-step state (and what that needs) has to run before S_t is fetched;
+                    # everything else waits, so that little more than a few vectors lives across the fetch
+                    early = set(g_bw2.depends_on(alias_next)) - set(alias_next)
+                    names = {n.name for n in g_bw2.nodes}
+                    for n in reversed(g_bw2.nodes):
+                        if n.name in early:
+                            early.update(a for a in n.value_args() if a in names)
+                    phase1 = [n for n in g_bw2.nodes if n.name in early]
+                    phase2 = [n for n in g_bw2.nodes if n.name not in early]
+                else:
+                    phase1 = [n for n in g_bw2.nodes if n.name not in dep_cur]
+                    phase2 = [n for n in g_bw2.nodes if n.name in dep_cur]
+                # a product is only folded into a consumer of its own part: between the parts the state
+                # registers change from S_{t+1} to S_t
+                sub.fuse_group(phase1, g_bw2.nodes, g_bw2.outputs)
+                sub.fuse_group(phase2, g_bw2.nodes, g_bw2.outputs)
+            else:
+                sub.fuse_group(g_bw2.nodes, g_bw2.nodes, set(g_bw2.outputs))
+            step_parts.update(sub=sub, phase1=phase1, phase2=phase2)
+        return step_parts["sub"]
+
+    def part_inputs(nodes: Sequence[Node], extra: Iterable[str] = ()) -> set:
+        names = set(extra)
+        for n in nodes:
+            names.update(n.value_args())
+        return names
+
+    def read_wk_named(sub: Body, names: set):
+        used_g = dict(zip(g_bw2.inputs, g_bw2.used_inputs()))
+        for nm in g_bw2.inputs:
+            if nm in kb.wk and used_g.get(nm, False) and nm in names:
+                kb.emit_wk_read(sub, nm, "wkt")
+
+    def crossing_values() -> List[Node]:
+        """Values of part 1 that part 2 or the outputs read: they live across the fetch of S_t."""
+        step_body()
+        later = part_inputs(step_parts["phase2"], g_bw2.outputs)
+        return [n for n in step_parts["phase1"] if n.name in later and n.name not in step_parts["sub"].fused]
+
+    def emit_part1(tlexpr: str):
+        """Split mode: part 1 of the step at chunk position ``tlexpr``; the state registers hold S_{t+1}."""
+        sub = step_body()
+        w.open("")
+        w(f"const int tl = {tlexpr}, t = t0 + tl; (void)t;")
+        w(f"const float* wkt = wkc + tl * {kb.wk_row}; (void)wkt;")
+        read_wk_named(sub, part_inputs(step_parts["phase1"]))
+        for n in step_parts["phase1"]:
+            sub.node(n, True)
+        w.close()
+
     def emit_bw_step():
-        """The backward step proper; expects tl, t, wkt in scope."""
-        sub = body.child()
-        read_wk_inputs(sub, g_bw2)
-        if alias_next:
-            # phase 1 (state registers hold S_{t+1}): every node that does not need S_t
-            for k, nm in enumerate(alias_next):
-                sub.alias[nm] = p.st_names[k]
-                sub.shape[nm] = stcls
-            dep_cur = g_bw2.depends_on(p.st_names)
-            phase1 = [n for n in g_bw2.nodes if n.name not in dep_cur]
-            phase2 = [n for n in g_bw2.nodes if n.name in dep_cur]
-            # a product is only folded into a consumer of its own phase: between the phases the state
-            # registers change from S_{t+1} to S_t
-            sub.fuse_group(phase1, g_bw2.nodes, g_bw2.outputs)
-            for n in phase1:
+        """The backward step proper; expects tl, t, wkt in scope (split mode: its second part and the outputs)."""
+        sub = step_body()
+        if split:
+            read_wk_named(sub, part_inputs(step_parts["phase2"], g_bw2.outputs))
+            for n in step_parts["phase2"]:
+                sub.node(n, True)
+        elif alias_next:
+            read_wk_inputs(sub, g_bw2)
+            for n in step_parts["phase1"]:
                 sub.node(n, True)
             emit_unstep()
-            sub.fuse_group(phase2, g_bw2.nodes, g_bw2.outputs)
-            for n in phase2:
+            for n in step_parts["phase2"]:
                 sub.node(n, True)
         else:
+            read_wk_inputs(sub, g_bw2)
             if rev:
                 emit_unstep()
-            sub.graph(g_bw2, allow_over_m=True)
+            for n in g_bw2.nodes:
+                sub.node(n, True)
         outs = g_bw2.outputs
         if redw:
             w.open("if (rcnt == 0)")
@@ -1962,6 +2057,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             o = outs[nin + k]
             sub.loops(stcls, lambda r, c, k=k, o=o: f"{body.at(dnext_names[k], r, c)} = {sub.at(o, r, c)};")
 
+    if split:
+        # values of the step's first part that its second part reads live across the fetch of S_t
+        for n in crossing_values():
+            body.declare(n.name, n.shape)
+            step_parts["sub"].predeclared.add(n.name)
+            step_parts["sub"].shape[n.name] = n.shape
     # ------------------------------------------------------------------ chunk loop
     w("#pragma unroll 1")
     w.open(f"for (int c = 0; c < {nchunk}; c++)")
@@ -2013,6 +2114,15 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     else:
         w(f"const int par = c & 1, nseg = (nv + {seg - 1}) / {seg}; (void)par;")
         w(f"#define PHYS(j) (par ? ({nphys - 1} - (j)) : (j))")
+        if split:
+            # the state registers hold the post-step state of the chunk's last step: the final state (first chunk
+            # handled) or the pre-step state of the step handled just before
+            w.open("if (c == 0)")
+            for k in range(ns):
+                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, str(nck))])
+                kb.emit_tile_global(vname(p.st_names[k]), ckspec, f"ck{k}", base, 3, 4, load=True)
+            w.close()
+            emit_part1("nv - 1")
         if ck_tma:
             w(f"if (!frnn_mbar_wait(&full[{B_CK}], c & 1, err, {ERR_CKPT_TIMEOUT})) return;")
         elif ws:
@@ -2067,6 +2177,10 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w("}")
         elif redw:
             emit_flush()
+        if split:
+            w.open(f"if (j * {seg} + i > 0)")
+            emit_part1(f"j * {seg} + i - 1")
+            w.close()
         w.close()   # i loop
         w.close()   # if j < nseg
         if not tm:
@@ -2119,4 +2233,4 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,
                          "reverse": rev, "hoisted": [n.name for n in kb.hoisted], "tile": [t.R, t.C, t.MB],
                          "packed": bool(pack2), "helper_warps": helper_warps, "tmem_cols": tm_cols if tm else 0,
-                         "seg": seg, "nslots": nslots}, kb.tmaps)
+                         "seg": seg, "nslots": nslots, "post_split": split}, kb.tmaps)

@@ -103,6 +103,8 @@ class Tuning:
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     fw_variant: int = -1     # >= 0: use this member of forward_variants(plan) untimed (tests, reproducible runs)
     bw_variant: int = -1     # >= 0: use this member of backward_variants(plan) untimed
+    bw_split: int = 1        # generic backward: evaluate the part of a step that needs only the post-step state while the
+                             # registers still hold it (from the step handled before) instead of recomputing that state
     bw_tmem: int = 1         # generic backward: keep the segment bases in Tensor Memory when they fit (more slots than
                              # shared memory holds, hence fewer recomputed steps); needs helper warps
     bw_tmem_slots: int = 0   # set by the planner: slots kept in Tensor Memory (0 = shared-memory slots)
@@ -202,6 +204,7 @@ class Plan:
     k_fwd: int
     k_joint: int
     reverse: Optional[lower.Reverse] = None
+    post_split: bool = False      # generic backward reads the post-step state from the registers (see lower.emit_backward)
     bw_choice: Tuple[int, int, int] = (4, 1, 2)   # (seg or reverse stage, kflush, ring buffers) that fit shared memory
 
 
@@ -354,11 +357,13 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             return [(k, 2) for k in ks] + [(k, 1) for k in ks]
         return [(k, b) for k in ks for b in (2, 1)]
 
+    post_split = bool(tu.bw_split) and reverse is None and lower.can_split_post(g_re, g_bw, list(st_names))
+
     def fits(sg, nsl, kflush, bufs, helper, tmem=0):
         try:
             ks = emit_backward(prob, g_re, g_bw, aux, nout, grads, dy_names, dnext_names, bw_tile, sg, nsl,
                                tu.use_tma, "", kflush=kflush, ring_bufs=bufs, reverse=reverse, helper_warps=helper,
-                               min_blocks=max(1, tu.bw_min_blocks), tmem_slots=tmem)
+                               min_blocks=max(1, tu.bw_min_blocks), tmem_slots=tmem, post_split=post_split)
         except lower.LoweringError:
             if tmem:
                 return False
@@ -416,7 +421,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         nck = (T + D - 1) // D + 1          # plus the final state
     else:
         D = choice[0] * tu.nslots
-        nck = (T + D - 1) // D
+        nck = (T + D - 1) // D + (1 if post_split else 0)     # plus the final state
 
     dev = inputs[0].device if inputs else state[0].device
     # declared outputs (what the fake implementations materialise)
@@ -428,7 +433,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     bw_meta = get_meta([*dx_meta, *stT_meta])
 
     plan = Plan(prob, joint, g_fw, g_re, g_bw, aux, nout, nst, grads, tu, fw_tile, bw_tile, D, nck,
-                g_fw0.count_mn_ops(), joint.pruned(jout, "all").count_mn_ops(), reverse, choice)
+                g_fw0.count_mn_ops(), joint.pruned(jout, "all").count_mn_ops(), reverse, post_split, choice)
     plan.dy_names, plan.dnext_names = dy_names, dnext_names   # type: ignore[attr-defined]
     plan.n_sm = n_sm                                            # type: ignore[attr-defined]
     return plan, fw_meta, bw_meta
@@ -446,7 +451,7 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Option
     stage = max(1, min(stage or tu.fw_stage, p.T))
     while True:
         fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, tile, stage, plan.D, tu.use_tma,
-                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None,
+                          tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None or plan.post_split,
                           step_unroll=unroll or tu.fw_unroll, pack2=pack2, col_major=bool(tu.col_major),
                           max_acc=tu.fw_acc)
         ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
@@ -510,7 +515,8 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
                            plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
                            kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
                            min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major),
-                           helper_warps=tu.bw_helper, max_acc=tu.bw_acc, tmem_slots=tu.bw_tmem_slots)
+                           helper_warps=tu.bw_helper, max_acc=tu.bw_acc, tmem_slots=tu.bw_tmem_slots,
+                           post_split=plan.post_split)
         if bw.smem_bytes <= _bw_smem_limit(tu):
             return bw
     return None

@@ -70,9 +70,11 @@ def test_full_size_slices(op_name, B, T, H, M, N, slices):
     shared = [i for i, x in enumerate(xs_cpu[:-1]) if x.shape[0] == 1 or x.shape[1] == 1]
     if shared:
         # all batch elements of one head: the gradient of a per-head input sums over them
+        # (fp64 leaves holding the same bf16 values: autograd would otherwise add the per-step contributions
+        # to a bf16 leaf in bf16, which is good to a few per cent only over 8192 terms)
         h = slices[1][1]
-        sl = [x[:, :, h:h + 1] if x.dim() == 5 else x[:, h:h + 1] for x in xs_cpu]
-        _, _, rgx, _ = O.fwd_bwd(O.STEPS[op_name], sl[:-1], sl[-1:], [dy_cpu[:, :, h:h + 1].float()],
-                                 [dS_cpu[:, h:h + 1].float()], dtype=torch.float64)
+        sl = [(x[:, :, h:h + 1] if x.dim() == 5 else x[:, h:h + 1]).double() for x in xs_cpu]
+        _, _, rgx, _ = O.fwd_bwd(O.STEPS[op_name], sl[:-1], sl[-1:], [dy_cpu[:, :, h:h + 1].double()],
+                                 [dS_cpu[:, h:h + 1].double()], dtype=torch.float64)
         for i in shared:
             assert O.rel_err(grads[i][:, :, h:h + 1], rgx[i]) < 1e-2, (op_name, "shared input", i)
