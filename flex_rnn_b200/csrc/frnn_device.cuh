@@ -105,7 +105,11 @@ FRNN_DEV float frnn_shfl_xor(float v, int off) { return __shfl_xor_sync(0xffffff
 FRNN_DEV void frnn_block_sync() { __syncthreads(); }
 FRNN_DEV void frnn_warp_sync() { __syncwarp(); }
 FRNN_DEV void frnn_atomic_add(float* p, float v) { atomicAdd(p, v); }
-FRNN_DEV void frnn_report(int* err, int code) { atomicCAS(err, 0, code); }
+// the error word may live in pinned host memory: a plain store reaches it (the first report is kept when it can be)
+FRNN_DEV void frnn_report(int* err, int code) {
+    if (*(volatile int*)err == 0) *(volatile int*)err = code;
+    __threadfence_system();
+}
 FRNN_DEV float frnn_expf(float x) { return __expf(x); }
 FRNN_DEV float frnn_logf(float x) { return __logf(x); }
 FRNN_DEV float frnn_sqrtf(float x) { return __fsqrt_rn(x); }

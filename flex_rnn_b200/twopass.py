@@ -126,23 +126,24 @@ def sm_count(device) -> int:
 
 
 class _DeviceStatus:
-    """The error word the kernels of one device report through, and a pinned
-    host mirror of it.  After every launch the word is copied to the mirror
-    behind the kernel on the same stream (no wait); the next call looks at the
-    mirror first and raises if a kernel of an earlier call gave up on a wait,
-    which costs the hot path no synchronisation."""
+    """The error word the kernels of one device report through.  It lives in pinned host memory, which the
+    device reaches directly (unified addressing): a kernel writes it only when one of its bounded waits ran out,
+    and the host looks at it before the next launch, so the report costs the hot path neither a copy nor a
+    synchronisation (a device-to-host copy per launch would queue behind a caller's own large transfers)."""
 
     def __init__(self, device):
-        self.word = th.zeros(1, dtype=th.int32, device=device)
-        self.host = th.zeros(1, dtype=th.int32).pin_memory()
+        self.device = device
+        self.word = th.zeros(1, dtype=th.int32).pin_memory()
 
-    def check(self, stream: int):
+    def check(self):
+        """Raise if a kernel launched earlier on this device reported a timed-out wait; clears the word."""
         from . import runtime
-        runtime.status_check(self.host.data_ptr(), self.word.data_ptr(), stream)
+        runtime.status_check(self.word.data_ptr(), 0, 0)
 
-    def post(self, stream: int):
-        from . import runtime
-        runtime.status_post(self.word.data_ptr(), self.host.data_ptr(), stream)
+    def check_now(self, stream: int):
+        """Wait for ``stream`` and check."""
+        th.cuda.current_stream(self.device).synchronize()
+        self.check()
 
 
 _status: Dict[int, _DeviceStatus] = {}
@@ -736,19 +737,13 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         """Raise if a kernel launched by an earlier call on this device reported
         a timed-out wait (its outputs were not valid).  No synchronisation."""
         if not emulated:
-            device_status(device).check(th.cuda.current_stream(device).cuda_stream)
+            device_status(device).check()
 
     def check_status(device, what):
-        """After a launch: queue the copy of the error word to its host mirror
-        (read by the next call).  With FRNN_CHECK=1 also wait and raise now."""
-        if emulated:
-            return
-        from . import runtime
-        stream = th.cuda.current_stream(device).cuda_stream
-        if strict:
-            runtime.status(device_status(device).word.data_ptr(), stream)
-        else:
-            device_status(device).post(stream)
+        """With FRNN_CHECK=1: wait for the launch and raise now if it reported a timed-out wait (off by
+        default, it serialises; by default the next call reports it)."""
+        if strict and not emulated:
+            device_status(device).check_now(th.cuda.current_stream(device).cuda_stream)
 
     def check_align(ts, flags, what):
         for i, (t, f) in enumerate(zip(ts, flags)):
@@ -881,7 +876,10 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         if emulated:
             return int(emu_words["w"].item()) if "w" in emu_words else 0
         idx = device.index if device.index is not None else th.cuda.current_device()
-        return int(_status[idx].word.item()) if idx in _status else 0
+        if idx not in _status:
+            return 0
+        th.cuda.synchronize(idx)
+        return int(_status[idx].word.item())
 
     forward.plan = plan                     # type: ignore[attr-defined]
     forward.sources = (fw_src, bw_src)      # type: ignore[attr-defined]

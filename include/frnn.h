@@ -106,7 +106,10 @@ int frnn_tensor_map_encode(void* out_map, const void* base, unsigned elt_bytes, 
  * `int` error word it was given as its last pointer parameter and returns
  * early, so its outputs are not valid.  (The reference has no counterpart: its
  * stubs check nothing, flex_rnn/to_cuda.py:245-252.)  The word is sticky until
- * one of the calls below clears it.
+ * one of the calls below clears it.  It may live in device memory or in pinned
+ * host memory, which the device writes directly under unified addressing; the
+ * Python host side uses the latter and calls frnn_status_check(word, NULL, NULL)
+ * before each launch, which needs neither a copy nor a wait.
  *
  * frnn_status:       copies the word to the host on `stream`, waits for the
  *                    stream, and returns FRNN_E_KERNEL (word cleared, message

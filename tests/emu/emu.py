@@ -28,17 +28,42 @@ def _wrapper(ks) -> str:
             f"  emu_launch([](void** args) {{ {ks.name}({', '.join(casts)}); }}, grid, nthreads, smem, args);\n}}\n")
 
 
+_FLAGS = ["-std=c++20", "-O1", "-fPIC", "-pthread", "-Wno-unknown-pragmas", "-Wno-attributes"]
+_pch_dir = None
+
+
+def _precompiled_header() -> str:
+    """Directory holding a copy of frnn_emu.h and its precompiled form (parsing <barrier>, <thread> and friends is
+    most of a kernel's build time otherwise).  Keyed by the header's contents; built once per cache."""
+    global _pch_dir
+    if _pch_dir is None:
+        text = open(os.path.join(HERE, "frnn_emu.h")).read()
+        d = os.path.join(_CACHE, "pch_" + hashlib.sha256((text + " ".join(_FLAGS)).encode()).hexdigest()[:16])
+        gch = os.path.join(d, "frnn_emu.h.gch")
+        if not os.path.exists(gch):
+            os.makedirs(d, exist_ok=True)
+            with open(os.path.join(d, "frnn_emu.h"), "w") as f:
+                f.write(text)
+            tmp = gch + f".{os.getpid()}.tmp"
+            r = subprocess.run(["g++", *_FLAGS, "-x", "c++-header", "-o", tmp, os.path.join(d, "frnn_emu.h")],
+                               capture_output=True, text=True)
+            if r.returncode:
+                raise RuntimeError("emulation header build failed:\n" + r.stderr[-4000:])
+            os.replace(tmp, gch)
+        _pch_dir = d
+    return _pch_dir
+
+
 def compile_emu(ks):
     os.makedirs(_CACHE, exist_ok=True)
-    src = '#include <cstdio>\n#include "frnn_emu.h"\n' + ks.source + _wrapper(ks)
+    src = '#include "frnn_emu.h"\n' + ks.source + _wrapper(ks)
     key = hashlib.sha256((src + open(os.path.join(HERE, "frnn_emu.h")).read()).encode()).hexdigest()[:24]
     so = os.path.join(_CACHE, f"emu_{key}.so")
     if not os.path.exists(so):
         cpp = os.path.join(_CACHE, f"emu_{key}.cpp")
         with open(cpp, "w") as f:
             f.write(src)
-        cmd = ["g++", "-std=c++20", "-O1", "-shared", "-fPIC", "-pthread", "-Wno-unknown-pragmas", "-Wno-attributes",
-               "-I", HERE, "-o", so + ".tmp", cpp]
+        cmd = ["g++", *_FLAGS, "-shared", "-I", _precompiled_header(), "-o", so + ".tmp", cpp]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             raise RuntimeError("emulation build failed:\n" + r.stderr[-4000:])

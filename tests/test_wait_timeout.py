@@ -3,11 +3,11 @@ stage never arrives the kernel records an error code and returns instead of
 spinning.  Exercised here with the prelude's own wait on an mbarrier that
 nothing completes and a 2 ms limit; the context stays usable afterwards.
 
-The report reaches the caller without any debugging switch: each launch of the
-library is followed by an asynchronous copy of the device's error word to a
-pinned host mirror, and the next forward or backward call looks at the mirror
-before it launches and raises (frnn_status_post / frnn_status_check of the C
-ABI).  The synchronous form, frnn_status, returns FRNN_E_KERNEL directly."""
+The report reaches the caller without any debugging switch: the library's
+error word lives in pinned host memory that the kernels write directly, and
+the next forward or backward call looks at it before it launches and raises
+(frnn_status_check of the C ABI).  For a word in device memory frnn_status
+copies, waits and returns FRNN_E_KERNEL; frnn_status_post queues the copy."""
 import pytest
 import torch
 
@@ -81,7 +81,6 @@ def test_timed_out_wait_raises_at_the_next_call():
         y0, S0 = op(*xs)
         st = twopass.device_status("cuda:0")
         mod, done = _timed_out_kernel(st.word.data_ptr())          # reports through the library's own word
-        y1, _ = op(*xs)          # launches fine; the copy of the word to its host mirror follows the kernel
         torch.cuda.synchronize()
         assert int(done.item()) == 2
         with pytest.raises(runtime.FrnnError, match="reported error 7"):
