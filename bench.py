@@ -680,6 +680,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the benchmark's 8); smaller = profiling case")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--probe-only", action="store_true",
+                    help="only run the library's FP32 probe kernels (peak and the scan kernels' kinds of FMA) and print their rates")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the records beside the headline (other workloads, scaling configuration, reference CUDA)")
     args = ap.parse_args()
@@ -694,7 +696,11 @@ def main():
     if args.gpus != world:
         sys.exit(f"bench.py: --gpus {args.gpus} but {world} process(es) were launched; for N > 1 start it with "
                  f"`python -m torch.distributed.run --nnodes=1 --nproc-per-node {args.gpus} bench.py --gpus {args.gpus} ...`")
-    if args.impl == "reference":
+    if args.probe_only:
+        b = Bench(args, rank, world, local)
+        peak = b.probe_fp32_peak()
+        print(json.dumps({"fp32_peak_tflops": peak, "sms": b.sms, "fp32_pipe_share_by_fma_kind": b.probe_fma_kinds()}), flush=True)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     elif args.impl == "reference_cuda":
         run_reference_cuda(args, rank, world, local)

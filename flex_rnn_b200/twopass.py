@@ -450,6 +450,14 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Option
     tile = tile or plan.fw_tile
     # keep the per-CTA shared memory small enough for all CTAs of an SM to be resident
     stage = max(1, min(stage or tu.fw_stage, p.T))
+    if unroll is None:
+        # keep the unrolled step loop inside the instruction cache: about 0.55 instructions of 16 bytes per counted
+        # [M,N] operation and tile element, plus the per-step overhead (measured: a 52 KB loop body runs at half the
+        # speed of a 26 KB one, 40 KB is still fine)
+        step_bytes = 16 * (0.55 * plan.k_fwd * tile.R * tile.C * (0.6 if pack2 else 1.0) + 120)
+        unroll = tu.fw_unroll
+        while unroll > 1 and unroll * step_bytes > 40 * 1024:
+            unroll //= 2
     while True:
         fw = emit_forward(p, plan.g_fw, plan.aux, plan.n_out, tile, stage, plan.D, tu.use_tma,
                           tu.fw_min_blocks, prelude(), final_ckpt=plan.reverse is not None or plan.post_split,
@@ -486,6 +494,7 @@ def forward_variants(plan: Plan) -> List[dict]:
     default_pack = bool(plan.tuning.pack2 & 2)
     out = [dict(tile=t, pack=default_pack, stage=None, unroll=None) for t in forward_tile_candidates(plan)]
     out.append(dict(tile=plan.fw_tile, pack=not default_pack, stage=None, unroll=None))
+    out.append(dict(tile=plan.fw_tile, pack=default_pack, stage=None, unroll=1))
     if plan.reverse is None and plan.D <= 16:
         # one chunk per checkpoint interval, step loop fully unrolled
         out.append(dict(tile=plan.fw_tile, pack=default_pack, stage=plan.D, unroll=plan.D))
