@@ -765,8 +765,10 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
              "launch_bw": launch_bw, "bw_src": bw_src,
              "fw_choice": max(0, tu0.fw_variant), "bw_choice": max(0, tu0.bw_variant), "fw_log": [], "bw_log": []}
 
-    def timed(launcher, ptrs, device, reps=3):
-        """Median device time of ``reps`` launches after one warm-up launch (which also compiles)."""
+    def timed(launcher, ptrs, device, reps=5):
+        """Median device time of ``reps`` launches after two warm-up launches (the first also compiles, and the
+        GPU's clocks have dropped while the compiler ran)."""
+        launcher(ptrs, device)
         launcher(ptrs, device)
         ms = []
         for _ in range(reps):
