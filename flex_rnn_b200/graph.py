@@ -107,6 +107,83 @@ class StepGraph:
                 k += 1
         return k
 
+    def simplified_products(self) -> "StepGraph":
+        """The same function with fewer full-tile operations, by two rewrites that only reassociate products:
+
+        * a sum of an outer product, ``sum(a[M,1] * b[1,N])``, is a vector times a sum:
+          over rows ``b * sum(a)``, over columns ``a * sum(b)``;
+        * a product of a tile with two lower-rank factors in a row, ``(T * s) * y``, is ``T * (s * y)`` when
+          ``s * y`` is itself lower-rank and ``T * s`` has no other use.
+
+        (Rounding differs in the last bit from the unsimplified order.)"""
+        nodes = [Node(n.name, n.op, list(n.args), n.shape, n.over_m, n.over_n) for n in self.nodes]
+        shape = dict(self.shape)
+        fresh = [0]
+
+        def new_name(base: str) -> str:
+            fresh[0] += 1
+            return f"{base}_r{fresh[0]}"
+
+        def join(a: Shape, b: Shape) -> Shape:
+            return (max(a[0], b[0]), max(a[1], b[1]))
+
+        changed = True
+        while changed:
+            changed = False
+            uses: Dict[str, int] = {}
+            for n in nodes:
+                for a in n.value_args():
+                    uses[a] = uses.get(a, 0) + 1
+            for o in self.outputs:
+                uses[o] = uses.get(o, 0) + 1
+            by_name = {n.name: n for n in nodes}
+            for idx, n in enumerate(nodes):
+                # sum of an outer product
+                if n.op == "sum" and isinstance(n.args[0], str) and n.args[0] in by_name and uses.get(n.args[0], 0) == 1:
+                    pr = by_name[n.args[0]]
+                    if pr.op == "mul" and pr.shape == MN and all(isinstance(a, str) for a in pr.args):
+                        sa, sb = shape[pr.args[0]], shape[pr.args[1]]
+                        if {sa, sb} == {M1, N1}:
+                            a_m = pr.args[0] if sa == M1 else pr.args[1]
+                            b_n = pr.args[1] if sa == M1 else pr.args[0]
+                            repl: List[Node] = []
+                            fa, fb = a_m, b_n
+                            if n.over_m:
+                                fa = new_name(n.name)
+                                repl.append(Node(fa, "sum", [a_m], S11, True, False))
+                                shape[fa] = S11
+                            if n.over_n:
+                                fb = new_name(n.name)
+                                repl.append(Node(fb, "sum", [b_n], S11, False, True))
+                                shape[fb] = S11
+                            repl.append(Node(n.name, "mul", [fa, fb], n.shape))
+                            nodes[idx:idx + 1] = repl
+                            nodes.remove(pr)
+                            changed = True
+                            break
+                # (T * s) * y  ->  T * (s * y)
+                if n.op == "mul" and n.shape == MN and all(isinstance(a, str) for a in n.args):
+                    for k in (0, 1):
+                        x, y = n.args[k], n.args[1 - k]
+                        m1 = by_name.get(x)
+                        if (m1 is None or m1.op != "mul" or m1.shape != MN or uses.get(x, 0) != 1 or shape[y] == MN
+                                or not all(isinstance(a, str) for a in m1.args)):
+                            continue
+                        for j in (0, 1):
+                            tile, s = m1.args[j], m1.args[1 - j]
+                            if shape[tile] == MN and shape[s] != MN and join(shape[s], shape[y]) != MN:
+                                sy = new_name(n.name)
+                                shape[sy] = join(shape[s], shape[y])
+                                nodes[idx:idx + 1] = [Node(sy, "mul", [s, y], shape[sy]), Node(n.name, "mul", [tile, sy], MN)]
+                                nodes.remove(m1)
+                                changed = True
+                                break
+                        if changed:
+                            break
+                    if changed:
+                        break
+        return StepGraph(self.name, list(self.inputs), nodes, list(self.outputs), shape)
+
     def code(self) -> str:
         """Readable listing (debugging aid)."""
         tag = {MN: "MN", M1: "M1", N1: "1N", S11: "11"}

@@ -1446,6 +1446,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         g_bw = g_bw.pruned(g_bw.outputs, g_bw.name, leaves=[n for n in ns_names if n not in g_bw.inputs])
         alias_next = ns_names
         split = True
+    g_bw = g_bw.simplified_products()
     graphs = [g_bw] + ([reverse.graph] if rev else [g_re])
     used_lists = [g.used_inputs() for g in graphs]
     used = [any(u[i] for u in used_lists) for i in range(nin)]
