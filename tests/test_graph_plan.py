@@ -189,3 +189,59 @@ def test_dry_run_under_fake_tensors():
         fm, bm = build_twopass(X.mlstm_gates, (i, i), (torch.empty(2, 3, 1, 1, device="cuda"),), dryrun=True)
         assert [tuple(m[0]) for m in fm[:4]] == [(2, 7, 3, 1)] * 3 + [(2, 3, 1, 1)]
         assert [tuple(m[0]) for m in bm] == [(2, 7, 3, 1, 1)] * 2 + [(2, 3, 1, 1)]
+
+
+def test_backward_structure_at_benchmark_shapes():
+    """What the planner builds for the benchmark workloads: helper warps (a warpgroup beside the tile's
+    threads, registers rebalanced between the two), segment bases in Tensor Memory for the recomputing
+    backward (four of them: 10 re-steps per 8 steps), the post-step state taken from the registers, and the
+    reverse re-step without any of the recomputing machinery for the Delta Rule."""
+    for op, (M, N) in (("delta_rule", (128, 128)), ("gated_delta_rule", (128, 128)), ("rwkv7", (128, 128)), ("mamba2", (64, 128))):
+        ins, st = metas(op, 8, 1024, 32, M, N)
+        plan, fw_meta, _ = make_plan(W.STEPS[op], ins, st)
+        fw, bw = generate(plan)
+        src = bw.source.split('extern "C"')[-1]
+        assert bw.info["helper_warps"] == 4 and bw.block == bw.info["tile"][2] // bw.info["tile"][0] * (N // bw.info["tile"][1]) + 128
+        assert "frnn_regs_release<" in src and "frnn_regs_acquire<" in src and "frnn_mbar_arrive(" in src
+        assert "frnn_block_sync" not in src.split("frnn_block_sync();", 2)[-1]      # one block barrier, before the roles split
+        if op == "delta_rule":
+            assert plan.reverse is not None and bw.info["tmem_cols"] == 0 and not bw.info["post_split"]
+            assert plan.D == 64 and plan.nck == 1024 // 64 + 1
+        else:
+            assert plan.reverse is None and bw.info["post_split"] and plan.post_split
+            assert bw.info["tmem_cols"] == (512 if M == 128 else 256) and (bw.info["seg"], bw.info["nslots"]) == (2, 4)
+            assert "frnn_tmem_alloc(" in src and "frnn_tmem_dealloc(" in src and "frnn_tmem_st<64>" in src
+            assert plan.D == 8 and plan.nck == 1024 // 8 + 1                          # plus the final state
+            assert tuple(fw_meta[2][0]) == (8, 32, plan.nck, M, N)
+        assert bw.smem_bytes <= 227 * 1024
+
+
+def test_product_reassociation():
+    """(T * s) * y -> T * (s * y) and sum(a[M,1] * b[1,N]) -> vector * sum: same values, fewer full-tile ops."""
+    from flex_rnn_b200.graph import Node, StepGraph
+    g = StepGraph("t", ["T", "s", "y", "a", "b"], [
+        Node("m1", "mul", ["T", "s"], MN), Node("m2", "mul", ["m1", "y"], MN), Node("r", "sum", ["m2"], N1, True, False),
+        Node("o", "mul", ["a", "b"], MN), Node("q", "sum", ["o"], N1, True, False), Node("z", "add", ["r", "q"], N1)],
+        ["z"], {"T": MN, "s": S11, "y": M1, "a": M1, "b": N1, "m1": MN, "m2": MN, "r": N1, "o": MN, "q": N1, "z": N1})
+    h = g.simplified_products()
+    assert g.count_mn_ops() == 5 and h.count_mn_ops() == 2
+    vals = {"T": torch.randn(6, 5), "s": torch.randn(1, 1), "y": torch.randn(6, 1), "a": torch.randn(6, 1), "b": torch.randn(1, 5)}
+
+    def run(graph):
+        v = dict(vals)
+        for n in graph.nodes:
+            x = [v[a] for a in n.args]
+            if n.op == "mul":
+                v[n.name] = x[0] * x[1]
+            elif n.op == "add":
+                v[n.name] = x[0] + x[1]
+            else:
+                dims = [d for d, on in ((0, n.over_m), (1, n.over_n)) if on]
+                v[n.name] = x[0].sum(dims, keepdim=True)
+        return v[graph.outputs[0]]
+    assert torch.allclose(run(g), run(h), rtol=1e-5, atol=1e-6)
+    # a product with another use is left alone
+    g2 = StepGraph("t", ["T", "s", "y"], [Node("m1", "mul", ["T", "s"], MN), Node("m2", "mul", ["m1", "y"], MN),
+                                          Node("k", "add", ["m1", "m2"], MN)], ["k"],
+                   {"T": MN, "s": S11, "y": M1, "m1": MN, "m2": MN, "k": MN})
+    assert [n.name for n in g2.simplified_products().nodes] == ["m1", "m2", "k"]
