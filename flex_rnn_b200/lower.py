@@ -1351,7 +1351,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                   kflush: int = 1, ring_bufs: int = 2, reverse: Optional[Reverse] = None,
                   step_unroll: int = 2, min_blocks: int = 1, pack2: bool = False,
                   col_major: bool = False, helper_warps: int = 0, max_acc: int = 1,
-                  tmem_slots: int = 0, post_split: bool = False) -> KernelSource:
+                  tmem_slots: int = 0, post_split: bool = False, unroll_segment: int = 0) -> KernelSource:
     """Reverse-time kernel.
 
     ``g_re`` computes the new states from [*inputs, *states, *aux];
@@ -2139,7 +2139,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             tmem_rw("0", store=True)
         w("#pragma unroll 1")
         w.open("for (int j = 1; j < nseg; j++)")
-        w("#pragma unroll 1")
+        w("#pragma unroll" if unroll_segment else "#pragma unroll 1")
         w.open(f"for (int i = 0; i < {seg}; i++)")
         emit_restep(f"(j - 1) * {seg} + i")
         w.close()
@@ -2151,17 +2151,20 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         if tm:
             w("frnn_tmem_wait_st();")
         # phase B: walk the chunk backwards
-        w("#pragma unroll 1")
+        w("#pragma unroll" if unroll_segment >= 2 else "#pragma unroll 1")
         w.open(f"for (int j = {(nslots if tm else nphys) - 1}; j >= 0; j--)")
         w.open("if (j < nseg)")
         w(f"const int seglen = min({seg}, nv - j * {seg});")
-        w("#pragma unroll 1")
-        w.open("for (int i = seglen - 1; i >= 0; i--)")
+        # with ``unroll_segment`` the steps of a segment (and their re-steps) form one straight-line block
+        w("#pragma unroll" if unroll_segment else "#pragma unroll 1")
+        w.open(f"for (int i = {seg - 1}; i >= 0; i--)" if unroll_segment else "for (int i = seglen - 1; i >= 0; i--)")
+        if unroll_segment:
+            w.open("if (i < seglen)")
         if tm:
             tmem_rw("j", store=False)
         else:
             slot_rw("PHYS(j)", store=False)
-        w("#pragma unroll 1")
+        w("#pragma unroll" if unroll_segment else "#pragma unroll 1")
         w.open("for (int i2 = 0; i2 < i; i2++)")
         emit_restep(f"j * {seg} + i2")
         w.close()
@@ -2182,6 +2185,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w.open(f"if (j * {seg} + i > 0)")
             emit_part1(f"j * {seg} + i - 1")
             w.close()
+        if unroll_segment:
+            w.close()   # if i < seglen
         w.close()   # i loop
         w.close()   # if j < nseg
         if not tm:

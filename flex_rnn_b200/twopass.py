@@ -105,6 +105,8 @@ class Tuning:
     bw_variant: int = -1     # >= 0: use this member of backward_variants(plan) untimed
     bw_split: int = 1        # generic backward: evaluate the part of a step that needs only the post-step state while the
                              # registers still hold it (from the step handled before) instead of recomputing that state
+    bw_unroll_seg: int = 1   # generic backward: 1 = the steps of a segment (and their re-steps) form one straight-line
+                             # block (measured: Gated Delta 7 %, Mamba-2 4 % faster), 2 = the whole chunk does
     bw_tmem: int = 1         # generic backward: keep the segment bases in Tensor Memory when they fit (more slots than
                              # shared memory holds, hence fewer recomputed steps); needs helper warps
     bw_tmem_slots: int = 0   # set by the planner: slots kept in Tensor Memory (0 = shared-memory slots)
@@ -387,8 +389,10 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
             for helper in helpers:
                 # with helper warps a chunk boundary is cheap: prefer a long flush group over a long staged chunk
                 stages = [s for s in (16, 8, 4) if s <= tu.rev_stage] if helper else list(range(tu.rev_stage, 0, -1))
-                order = [(sg, fl) for fl in flush_options(helper) for sg in stages] if helper else \
-                        [(sg, fl) for sg in stages for fl in flush_options(helper)]
+                # ... and a staged chunk that is exactly one flush group first (one straight-line block of steps per
+                # chunk: measured 6 % faster than two groups per chunk for the Delta Rule)
+                order = [(sg, fl) for fl in flush_options(helper) for sg in sorted(stages, key=lambda s: (s != fl[0], -s))] \
+                    if helper else [(sg, fl) for sg in stages for fl in flush_options(helper)]
                 for sg, (kflush, bufs) in order:
                     if fits(sg, tu.nslots, kflush, bufs, helper):
                         return (sg, kflush, bufs), tu.nslots, helper
@@ -525,7 +529,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
                            kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
                            min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major),
                            helper_warps=tu.bw_helper, max_acc=tu.bw_acc, tmem_slots=tu.bw_tmem_slots,
-                           post_split=plan.post_split)
+                           post_split=plan.post_split, unroll_segment=int(tu.bw_unroll_seg))
         if bw.smem_bytes <= _bw_smem_limit(tu):
             return bw
     return None
