@@ -1552,6 +1552,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"frnn_mbar_init(&full[{B_WKE}], {NCT}); frnn_mbar_init(&full[{B_WKE + 1}], {NCT});")
         w(f"frnn_mbar_init(&full[{B_RGF}], {NCT}); frnn_mbar_init(&full[{B_RGF + 1}], {NCT});")
         w(f"frnn_mbar_init(&full[{B_RGE}], {HT}); frnn_mbar_init(&full[{B_RGE + 1}], {HT});")
+        w(f"frnn_mbar_init(&full[11], {NCT}); frnn_mbar_init(&full[14], {HT});   // rendezvous of the compute / helper threads")
     if tm:
         w("((int*)&full[13])[0] = 0;      // warps that are done with Tensor Memory")
     w("frnn_mbar_init_fence();")
@@ -1572,8 +1573,14 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     nv_first = p.T - first_c * D
 
     def csync(why: str = ""):
-        """Barrier over the compute warps."""
-        w((f"frnn_group_sync(1, {NCT});" if ws else "frnn_block_sync();") + (f"   // {why}" if why else ""))
+        """Barrier over the compute warps.  With helper warps it is an mbarrier rendezvous with a bounded wait,
+        not a hardware barrier: should one warp leave on a timed-out wait, the others must not wait for it for ever."""
+        if not ws:
+            w("frnn_block_sync();" + (f"   // {why}" if why else ""))
+            return
+        w(f"frnn_mbar_arrive(&full[11]);" + (f"   // {why}" if why else ""))
+        w(f"if (!frnn_mbar_wait(&full[11], cs_par, err, {ERR_STAGE_TIMEOUT})) return;")
+        w("cs_par ^= 1;")
 
     # element offsets inside one ring row
     ring_off: Dict[int, int] = {}
@@ -1715,7 +1722,10 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         for i in const_inputs:
             if p.in_cls(i) == S11:      # time-invariant scalars feed hoisted nodes: the helpers evaluate those
                 kb.emit_const_input(hbody, p.in_names[i], S11, p.inputs[i], f"in{i}", IN_DIMS)
-        hsync = "frnn_warp_sync();" if helper_warps == 1 else f"frnn_group_sync(2, {HT});"
+        # rendezvous of the helper threads (bounded, like the compute warps')
+        hsync = "frnn_warp_sync();" if helper_warps == 1 else (
+            f"frnn_mbar_arrive(&full[14]); if (!frnn_mbar_wait(&full[14], hs_par, err, {ERR_STAGE_TIMEOUT})) return; hs_par ^= 1;")
+        w("u32 hs_par = 0; (void)hs_par;")
         emit_racc_decl()
         w("int hg = 0; (void)hg;   // flush groups served so far")
 
@@ -1829,6 +1839,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     if not ws:
         emit_racc_decl()
     w("int rcnt = 0, rhalf = 0, rt_first = 0, gidx = 0; (void)rcnt; (void)rhalf; (void)rt_first; (void)gidx;")
+    w("u32 cs_par = 0; (void)cs_par;")
 
     def emit_flush():
         """The collected steps are complete: reduce them over the row groups and write the gradients
