@@ -210,26 +210,94 @@ FRNN_DEV bool frnn_mbar_wait(u64* bar, u32 parity, int* err, int code) {
     }
 }
 
+// ---- checked build (-DFRNN_BOUNDS) ------------------------------------------
+// A debugging build of a generated kernel in which every load, store, atomic add
+// and 1-D bulk copy first checks that its whole byte range lies inside one of the
+// kernel's buffers (the generator registers each pointer parameter with the byte
+// extent it derived from the tensor's shape and strides) or inside the CTA's
+// dynamic shared memory.  An access outside is not performed: a load yields
+// zeros, a store is dropped, and FRNN_ERR_BOUNDS goes to the error word, so that
+// an indexing mistake shows up as an error code instead of a memory fault.
+// Tiled tensor-map loads need no check (the hardware zero-fills outside the map).
+#define FRNN_ERR_BOUNDS 64
+#ifdef FRNN_BOUNDS
+#define FRNN_BOUNDS_MAX 48
+struct frnn_bounds_t {
+    const char* lo[FRNN_BOUNDS_MAX];
+    const char* hi[FRNN_BOUNDS_MAX];
+    const char* smem_lo;
+    const char* smem_hi;
+    int* err;
+    int n;
+};
+#ifdef FRNN_EMU
+static frnn_bounds_t frnn_bounds_state;      // the emulation runs one CTA at a time
+#else
+__shared__ frnn_bounds_t frnn_bounds_state;  // one table per CTA
+#endif
+// thread 0 of the CTA, before the first access; the caller synchronises the CTA afterwards
+FRNN_DEV void frnn_bounds_begin(int* err, const void* smem, long smem_bytes) {
+    frnn_bounds_state.n = 0;
+    frnn_bounds_state.err = err;
+    frnn_bounds_state.smem_lo = (const char*)smem;
+    frnn_bounds_state.smem_hi = (const char*)smem + smem_bytes;
+}
+FRNN_DEV void frnn_bounds_add(const void* base, long bytes) {
+    const int i = frnn_bounds_state.n;
+    if (i < FRNN_BOUNDS_MAX && bytes > 0) {
+        frnn_bounds_state.lo[i] = (const char*)base;
+        frnn_bounds_state.hi[i] = (const char*)base + bytes;
+        frnn_bounds_state.n = i + 1;
+    }
+}
+FRNN_DEV bool frnn_access_ok(const void* p, long bytes) {
+    const char* a = (const char*)p;
+    if (a >= frnn_bounds_state.smem_lo && a + bytes <= frnn_bounds_state.smem_hi) return true;
+    for (int i = 0; i < frnn_bounds_state.n; i++)
+        if (a >= frnn_bounds_state.lo[i] && a + bytes <= frnn_bounds_state.hi[i]) return true;
+    frnn_report(frnn_bounds_state.err, FRNN_ERR_BOUNDS);
+    return false;
+}
+#define FRNN_ACCESS_OK(p, bytes) frnn_access_ok((const void*)(p), (long)(bytes))
+#else
+#define FRNN_ACCESS_OK(p, bytes) true
+#endif
+FRNN_DEV void frnn_atomic_add_c(float* p, float v) {
+    if (FRNN_ACCESS_OK(p, 4)) frnn_atomic_add(p, v);
+}
+FRNN_DEV void frnn_bulk_g2s_c(void* dst_smem, const void* src_gmem, u32 bytes, u64* bar) {
+    // a refused copy never completes its mbarrier: the waiting side runs into its time limit and leaves
+    if (FRNN_ACCESS_OK(src_gmem, bytes) && FRNN_ACCESS_OK(dst_smem, bytes)) frnn_bulk_g2s(dst_smem, src_gmem, bytes, bar);
+}
+// element i of an array of T, untranslated (the register-prefetched inputs)
+template <class T> FRNN_DEV T frnn_ld_raw(const void* p, long i) {
+    if (!FRNN_ACCESS_OK((const T*)p + i, sizeof(T))) return T(0);
+    return ((const T*)p)[i];
+}
+template <class T> FRNN_DEV void frnn_st_raw(void* p, long i, T v) {
+    if (FRNN_ACCESS_OK((T*)p + i, sizeof(T))) ((T*)p)[i] = v;
+}
+
 template <int DT> struct frnn_io;  // 0 = fp32, 1 = bf16, 2 = fp16, 3 = fp64
 template <> struct frnn_io<0> {
     typedef float T;
-    static FRNN_DEV float ld(const void* p, long i) { return ((const float*)p)[i]; }
-    static FRNN_DEV void st(void* p, long i, float v) { ((float*)p)[i] = v; }
+    static FRNN_DEV float ld(const void* p, long i) { return frnn_ld_raw<float>(p, i); }
+    static FRNN_DEV void st(void* p, long i, float v) { frnn_st_raw<float>(p, i, v); }
 };
 template <> struct frnn_io<1> {
     typedef u16 T;
-    static FRNN_DEV float ld(const void* p, long i) { return frnn_bf16_to_f32(((const u16*)p)[i]); }
-    static FRNN_DEV void st(void* p, long i, float v) { ((u16*)p)[i] = frnn_f32_to_bf16(v); }
+    static FRNN_DEV float ld(const void* p, long i) { return frnn_bf16_to_f32(frnn_ld_raw<u16>(p, i)); }
+    static FRNN_DEV void st(void* p, long i, float v) { frnn_st_raw<u16>(p, i, frnn_f32_to_bf16(v)); }
 };
 template <> struct frnn_io<2> {
     typedef u16 T;
-    static FRNN_DEV float ld(const void* p, long i) { return frnn_f16_to_f32(((const u16*)p)[i]); }
-    static FRNN_DEV void st(void* p, long i, float v) { ((u16*)p)[i] = frnn_f32_to_f16(v); }
+    static FRNN_DEV float ld(const void* p, long i) { return frnn_f16_to_f32(frnn_ld_raw<u16>(p, i)); }
+    static FRNN_DEV void st(void* p, long i, float v) { frnn_st_raw<u16>(p, i, frnn_f32_to_f16(v)); }
 };
 template <> struct frnn_io<3> {
     typedef double T;
-    static FRNN_DEV float ld(const void* p, long i) { return (float)((const double*)p)[i]; }
-    static FRNN_DEV void st(void* p, long i, float v) { ((double*)p)[i] = (double)v; }
+    static FRNN_DEV float ld(const void* p, long i) { return (float)frnn_ld_raw<double>(p, i); }
+    static FRNN_DEV void st(void* p, long i, float v) { frnn_st_raw<double>(p, i, (double)v); }
 };
 
 // sum over the L lanes (L a power of two <= 32) that share one state row
@@ -262,7 +330,15 @@ template <int DT> FRNN_DEV u32 frnn_pack16(float a, float b);
 template <> FRNN_DEV u32 frnn_pack16<1>(float a, float b) { return (u32)frnn_f32_to_bf16(a) | ((u32)frnn_f32_to_bf16(b) << 16); }
 template <> FRNN_DEV u32 frnn_pack16<2>(float a, float b) { return (u32)frnn_f32_to_f16(a) | ((u32)frnn_f32_to_f16(b) << 16); }
 
+template <int DT> struct frnn_esize { static const int v = DT == 0 ? 4 : (DT == 3 ? 8 : 2); };
 template <int DT, int CNT> FRNN_DEV void frnn_ldv(const void* base, long i, float* out) {
+#ifdef FRNN_BOUNDS
+    if (!FRNN_ACCESS_OK((const char*)base + i * frnn_esize<DT>::v, CNT * frnn_esize<DT>::v)) {
+#pragma unroll
+        for (int k = 0; k < CNT; k++) out[k] = 0.0f;
+        return;
+    }
+#endif
     if constexpr (DT == 0 && CNT == 4) {
         FRNN_ASSERT_ALIGNED((const float*)base + i, 16);
         frnn_f4 t = *(const frnn_f4*)((const float*)base + i);
@@ -294,6 +370,9 @@ template <int DT, int CNT> FRNN_DEV void frnn_ldv(const void* base, long i, floa
 }
 
 template <int DT, int CNT> FRNN_DEV void frnn_stv(void* base, long i, const float* v) {
+#ifdef FRNN_BOUNDS
+    if (!FRNN_ACCESS_OK((const char*)base + i * frnn_esize<DT>::v, CNT * frnn_esize<DT>::v)) return;
+#endif
     if constexpr (DT == 0 && CNT == 4) {
         frnn_f4 t; t.x = v[0]; t.y = v[1]; t.z = v[2]; t.w = v[3];
         FRNN_ASSERT_ALIGNED((float*)base + i, 16);

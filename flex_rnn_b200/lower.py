@@ -660,6 +660,13 @@ def _elem_off(spec: TensorSpec, dims: Sequence[Tuple[int, str]]) -> str:
     return " + ".join(terms) if terms else "0L"
 
 
+def _spec_bytes(spec: TensorSpec) -> int:
+    """Bytes from the tensor's first element to the end of its last one."""
+    if any(n == 0 for n in spec.shape):
+        return 0
+    return (1 + sum((n - 1) * s for n, s in zip(spec.shape, spec.stride) if n > 1)) * ELT[spec.dt]
+
+
 def _contig(shape: Sequence[int]) -> Tuple[int, ...]:
     st, acc = [], 1
     for s in reversed(shape):
@@ -699,15 +706,33 @@ class KernelBuilder:
         self.items: List[StagedItem] = []
         self.params: List[str] = []
         self.param_decl: List[str] = []
+        self.param_bytes: Dict[str, int] = {}
         self.const_scalars: Dict[str, str] = {}    # time-invariant [1,1] inputs kept in registers
         self.tensor_tma = True                     # use tiled tensor-map loads where possible
 
     # -- parameters ----------------------------------------------------------
-    def add_param(self, name: str, ctype: str, const: bool):
+    def add_param(self, name: str, ctype: str, const: bool, nbytes: int = 0):
+        """``nbytes``: how many bytes from the pointer on the kernel may touch
+        (what the checked build registers for this parameter)."""
         self.params.append(name)
         q = "const " if const else ""
         r = " __restrict__" if const else ""
         self.param_decl.append(f"{q}{ctype}*{r} {name}")
+        self.param_bytes[name] = int(nbytes)
+
+    def emit_bounds_prologue(self):
+        """Checked build only: thread 0 registers every pointer parameter with
+        its byte extent and the CTA's dynamic shared memory, then the CTA
+        synchronises.  ``@SMEM_BYTES@`` is filled in when the source is final."""
+        w = self.w
+        w("#ifdef FRNN_BOUNDS")
+        w.open("if (threadIdx.x == 0)")
+        w("frnn_bounds_begin(err, smem, @SMEM_BYTES@L);")
+        for name, nbytes in self.param_bytes.items():
+            w(f"frnn_bounds_add({name}, {nbytes}L);")
+        w.close()
+        w("frnn_block_sync();")
+        w("#endif")
 
     # -- raw staging plan ------------------------------------------------------
     def add_item(self, key: str, cls: Shape, spec: TensorSpec, ptr: str, dims: Dict[str, int], const_off: int = 0):
@@ -849,7 +874,7 @@ class KernelBuilder:
             w.open("switch (k)")
             for k, it in enumerate(flat):
                 e = ELT[it.dt]
-                w(f"case {k}: frnn_bulk_g2s(stage + {it.off} + tl * {it.rowb}, "
+                w(f"case {k}: frnn_bulk_g2s_c(stage + {it.off} + tl * {it.rowb}, "
                   f"(const unsigned char*){it.ptr} + ({it.base} + (long)(t0 + tl) * {it.stride_t}L) * {e}, "
                   f"{it.length * e}u, bar); break;")
             w.close()
@@ -882,8 +907,8 @@ class KernelBuilder:
             w.open(f"for (int q = 0; q < {cnt}; q++)")
             w(f"const int e = tid + q * {t.NT}, tl = e / {it.length}, j = e % {it.length};")
             w(f"pl{k}[q] = 0;")
-            w(f"if (tl < {nv}) pl{k}[q] = (({'const ' + CTYPE[it.dt]}*){it.ptr})"
-              f"[{it.base} + (long)({t0} + tl) * {it.stride_t}L + (long)j * {it.inner}L];")
+            w(f"if (tl < {nv}) pl{k}[q] = frnn_ld_raw<{CTYPE[it.dt]}>({it.ptr}, "
+              f"{it.base} + (long)({t0} + tl) * {it.stride_t}L + (long)j * {it.inner}L);")
             w.close()
 
     def emit_plain_direct(self, stage: str, t0: str, nv: str, tidv: str, nthr: int):
@@ -893,8 +918,8 @@ class KernelBuilder:
         for it in self.plain_items:
             w.open(f"for (int e = {tidv}; e < ({nv}) * {it.length}; e += {nthr})")
             w(f"const int tl = e / {it.length}, j = e % {it.length};")
-            w(f"(({CTYPE[it.dt]}*)({stage} + {it.off} + tl * {it.rowb}))[j] = (({'const ' + CTYPE[it.dt]}*){it.ptr})"
-              f"[{it.base} + (long)({t0} + tl) * {it.stride_t}L + (long)j * {it.inner}L];")
+            w(f"(({CTYPE[it.dt]}*)({stage} + {it.off} + tl * {it.rowb}))[j] = frnn_ld_raw<{CTYPE[it.dt]}>({it.ptr}, "
+              f"{it.base} + (long)({t0} + tl) * {it.stride_t}L + (long)j * {it.inner}L);")
             w.close()
 
     def emit_plain_store(self, stage: str):
@@ -1039,7 +1064,7 @@ class KernelBuilder:
                 if load:
                     w(f"{el} = frnn_io<{spec.dt}>::ld({ptr}, {idx});")
                 elif add:
-                    w(f"frnn_atomic_add((float*){ptr} + ({idx}), {el});")
+                    w(f"frnn_atomic_add_c((float*){ptr} + ({idx}), {el});")
                 else:
                     w(f"frnn_io<{spec.dt}>::st({ptr}, {idx}, {el});")
         w.close()
@@ -1085,7 +1110,7 @@ class KernelBuilder:
         if atomic:
             w("#pragma unroll")
             w.open(f"for (int r = 0; r < {t.R}; r++)")
-            w(f"frnn_atomic_add((float*){ptr} + ({idx0} + (long)(row0 + r) * {stride_m}L), {arr}[r]);")
+            w(f"frnn_atomic_add_c((float*){ptr} + ({idx0} + (long)(row0 + r) * {stride_m}L), {arr}[r]);")
             w.close()
         elif stride_m == 1 and aligned:
             cnt = _pick_cnt(t.R, dt, t.R)
@@ -1152,19 +1177,20 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     used = g.used_inputs()
     stcls = p.st_cls()
 
+    ck_bytes = p.B * p.H * ((p.T + dck - 1) // dck + (1 if final_ckpt else 0)) * p.M * p.N * 4
     for i, spec in enumerate(p.inputs):
         if used[i]:
-            kb.add_param(f"in{i}", "void", True)
+            kb.add_param(f"in{i}", "void", True, _spec_bytes(spec))
     for k in range(ns):
-        kb.add_param(f"s0_{k}", "void", True)
+        kb.add_param(f"s0_{k}", "void", True, _spec_bytes(p.states[k]))
     for j in range(n_out):
-        kb.add_param(f"out{j}", "void", False)
+        kb.add_param(f"out{j}", "void", False, p.B * p.T * p.H * p.M * ELT[p.out_dt[j]])
     for k in range(ns):
-        kb.add_param(f"sT_{k}", "void", False)
+        kb.add_param(f"sT_{k}", "void", False, _spec_bytes(p.states[k]))
     for k in range(ns):
-        kb.add_param(f"ck{k}", "float", False)
-    kb.add_param("aux", "float", False)
-    kb.add_param("err", "int", False)
+        kb.add_param(f"ck{k}", "float", False, ck_bytes)
+    kb.add_param("aux", "float", False, len(aux_names) * p.B * p.H * p.T * p.M * 4)
+    kb.add_param("err", "int", False, 4)
 
     const_inputs = _stage_inputs(kb, p, used, allow_mn=True)
     (g2,) = kb.plan([g])
@@ -1187,6 +1213,7 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
     w.open(f"{kname}({', '.join(kb.param_decl)})")
     w("FRNN_DYN_SMEM(smem);")
     kb.emit_thread_ids()
+    kb.emit_bounds_prologue()
     w("u64* full = (u64*)smem;")
     w(f"unsigned char* stage = smem + {BAR_BYTES};")
     w(f"float* wk = (float*)(smem + {off_wk});")
@@ -1301,7 +1328,8 @@ def emit_forward(p: Problem, g: StepGraph, aux_names: List[str], n_out: int, til
             base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, str(nck))])
             kb.emit_tile_global(vname(p.st_names[k]), ckspec, f"ck{k}", base, 3, 4, load=False)
     w.close()
-    return KernelSource(kname, w.text(), (p.M // t.MB, p.H, p.B), t.NT, smem_bytes, kb.params, kb.param_decl,
+    return KernelSource(kname, w.text().replace("@SMEM_BYTES@", str(smem_bytes)), (p.M // t.MB, p.H, p.B), t.NT, smem_bytes,
+                        kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "tma_items": len(kb.tma_items),
                          "plain_items": len(kb.plain_items), "nck": nck_store, "hoisted": [n.name for n in kb.hoisted],
                          "tile": [t.R, t.C, t.MB], "packed": bool(pack2)},
@@ -1459,19 +1487,19 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
 
     for i in range(nin):
         if used[i]:
-            kb.add_param(f"in{i}", "void", True)
+            kb.add_param(f"in{i}", "void", True, _spec_bytes(p.inputs[i]))
     for j in range(n_out):
-        kb.add_param(f"dy{j}", "void", True)
+        kb.add_param(f"dy{j}", "void", True, p.B * p.T * p.H * p.M * ELT[p.out_dt[j]])
     for k in range(ns):
-        kb.add_param(f"dsT_{k}", "void", True)
+        kb.add_param(f"dsT_{k}", "void", True, p.B * p.H * p.M * p.N * ELT[p.states[k].dt])
     for k in range(ns):
-        kb.add_param(f"ck{k}", "float", True)
-    kb.add_param("aux", "float", True)
+        kb.add_param(f"ck{k}", "float", True, p.B * p.H * nck_store * p.M * p.N * 4)
+    kb.add_param("aux", "float", True, p.naux * p.B * p.H * p.T * p.M * 4)
     for k in range(ns):
-        kb.add_param(f"ds0_{k}", "void", False)
+        kb.add_param(f"ds0_{k}", "void", False, _spec_bytes(p.states[k]))
     for go in grads:
-        kb.add_param(f"dx{go.index}", "void", False)
-    kb.add_param("err", "int", False)
+        kb.add_param(f"dx{go.index}", "void", False, _spec_bytes(go.spec))
+    kb.add_param("err", "int", False, 4)
 
     const_inputs = _stage_inputs(kb, p, used, allow_mn=True)
     ashape = (max(1, p.naux), p.B, p.H, p.T, p.M)
@@ -1536,6 +1564,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     w.open(f"{kname}({', '.join(kb.param_decl)})")
     w("FRNN_DYN_SMEM(smem);")
     kb.emit_thread_ids()
+    kb.emit_bounds_prologue()
     w("u64* full = (u64*)smem;        // mbarriers")
     w(f"unsigned char* stage = smem + {off_stage};")
     w(f"float* wk = (float*)(smem + {off_wk});")
@@ -1627,7 +1656,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             n_el = p.N if go.cls == N1 else 1
             w.open(f"if (j >= {cum} && j < {cum + n_el})")
             dims = [(0, "b"), (2, "h")] + ([(4, f"(j - {cum})")] if go.cls == N1 else [])
-            w(f"frnn_atomic_add((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
+            w(f"frnn_atomic_add_c((float*)dx{go.index} + ({_elem_off(go.spec, dims)}), racc[q]);")
             w.close()
             cum += n_el
         w.close()
@@ -1671,7 +1700,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 sn = go.spec.st(4)
                 if go.atomic:
                     w("#pragma unroll")
-                    w(f"for (int q = 0; q < {vw}; q++) frnn_atomic_add((float*)dx{go.index} + ({idx} + (long)(c0 + q) * {sn}L), a[q]);")
+                    w(f"for (int q = 0; q < {vw}; q++) frnn_atomic_add_c((float*)dx{go.index} + ({idx} + (long)(c0 + q) * {sn}L), a[q]);")
                 elif sn == 1 and go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % (vw * ELT[go.spec.dt]) == 0 for d in (0, 1, 2)):
                     w(f"frnn_stv<{go.spec.dt},{vw}>(dx{go.index}, {idx} + c0, a);")
                 else:
@@ -1694,7 +1723,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
                 w.open(f"if (si == {k})")
                 idx = _elem_off(go.spec, [(0, "b"), (1, "tt"), (2, "h")])
                 if go.atomic:
-                    w(f"frnn_atomic_add((float*)dx{go.index} + ({idx}), a);")
+                    w(f"frnn_atomic_add_c((float*)dx{go.index} + ({idx}), a);")
                 else:
                     w(f"frnn_io<{go.spec.dt}>::st(dx{go.index}, {idx}, a);")
                 w.close()
@@ -1796,7 +1825,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w(f"frnn_mbar_expect_tx(&full[{B_CK}], {ns * slot_bytes}u);")
             for k in range(ns):
                 base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
-                w(f"frnn_bulk_g2s(slots + ((long)({physexpr}) * {ns} + {k}) * {slot_elems}, ck{k} + {base}, {slot_bytes}u, &full[{B_CK}]);")
+                w(f"frnn_bulk_g2s_c(slots + ((long)({physexpr}) * {ns} + {k}) * {slot_elems}, ck{k} + {base}, {slot_bytes}u, &full[{B_CK}]);")
             w.close()
         else:
             for k in range(ns):
@@ -2244,7 +2273,8 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"frnn_tmem_dealloc(tm_base, {tm_cols}u);")
         w.close()
     w.close()
-    return KernelSource(kname, w.text(), (1, p.H, p.B), NCT + HT, smem_bytes, kb.params, kb.param_decl,
+    return KernelSource(kname, w.text().replace("@SMEM_BYTES@", str(smem_bytes)), (1, p.H, p.B), NCT + HT, smem_bytes,
+                        kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),
                          "nck": nck_store, "D": D, "dck": dck, "ck_tma": ck_tma, "kflush": kflush, "ring_bufs": ring_bufs,

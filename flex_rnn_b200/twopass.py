@@ -113,6 +113,8 @@ class Tuning:
     fw_acc: int = 2          # independent accumulators per kept element of a sum, forward kernel (measured: 2 is 3-6 %
                              # faster than 4 or 1 on the forward, 1 is 3 % faster than 2 or 4 on the backward)
     bw_acc: int = 1          # the same, backward kernel
+    bounds: int = 0          # 1 = checked build of both kernels: every access is tested against the extents of the
+                             # kernel's buffers, one outside is skipped and reported through the error word (debugging)
     use_tma: bool = True
 
 
@@ -125,6 +127,40 @@ def sm_count(device) -> int:
     if getattr(device, "type", None) == "cuda" and th.cuda.is_available():
         return th.cuda.get_device_properties(device).multi_processor_count
     return B200_SMS
+
+
+class _GuardedBuffers:
+    """Debugging allocator (environment ``FRNN_GUARD=1``): every buffer a kernel
+    writes (outputs, final states, checkpoints, saved row sums, gradients) is
+    carved out of a larger allocation with a band of a fixed byte pattern on
+    either side, and ``check`` (after the launch has finished) raises if a band
+    was touched: a store that left its buffer by up to ``BAND`` bytes shows up
+    here instead of silently corrupting a neighbouring tensor."""
+    BAND = 4096
+    FILL = 0xA5
+
+    def __init__(self):
+        self.live: List[Tuple[str, th.Tensor, int]] = []
+
+    def empty(self, what, shape, stride, dtype, device, zero=False):
+        esize = th.empty((), dtype=dtype).element_size()
+        extent = 0 if any(n == 0 for n in shape) else 1 + sum((n - 1) * s for n, s in zip(shape, stride))
+        nbytes = extent * esize
+        raw = th.full((2 * self.BAND + (nbytes + 255) // 256 * 256,), self.FILL, dtype=th.uint8, device=device)
+        body = raw[self.BAND:self.BAND + nbytes].view(dtype)
+        if zero:
+            body.zero_()
+        self.live.append((what, raw, nbytes))
+        return body.as_strided(tuple(shape), tuple(stride))
+
+    def check(self):
+        live, self.live = self.live, []
+        for what, raw, nbytes in live:
+            lo, hi = raw[:self.BAND], raw[self.BAND + nbytes:]
+            bad = int((lo != self.FILL).sum()) + int((hi != self.FILL).sum())
+            if bad:
+                side = "before" if int((lo != self.FILL).sum()) else "after"
+                raise RuntimeError(f"flex_rnn_b200: a kernel wrote {bad} byte(s) outside {what} ({side} the buffer)")
 
 
 class _DeviceStatus:
@@ -473,7 +509,15 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Option
         stage //= 2
     if fw.smem_bytes > SMEM_LIMIT:
         raise lower.LoweringError(f"kernel {fw.name} needs {fw.smem_bytes} bytes of shared memory (limit {SMEM_LIMIT})")
-    return fw
+    return _checked(fw, tu)
+
+
+def _checked(ks: lower.KernelSource, tu: Tuning) -> lower.KernelSource:
+    """The checked build of a kernel when ``Tuning.bounds`` asks for it."""
+    if not tu.bounds:
+        return ks
+    import dataclasses
+    return dataclasses.replace(ks, source="#define FRNN_BOUNDS 1\n" + ks.source, info={**ks.info, "bounds": True})
 
 
 def forward_tile_candidates(plan: Plan) -> List[lower.Tile]:
@@ -531,7 +575,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
                            helper_warps=tu.bw_helper, max_acc=tu.bw_acc, tmem_slots=tu.bw_tmem_slots,
                            post_split=plan.post_split, unroll_segment=int(tu.bw_unroll_seg))
         if bw.smem_bytes <= _bw_smem_limit(tu):
-            return bw
+            return _checked(bw, tu)
     return None
 
 
@@ -744,6 +788,25 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         return device_status(device).word
 
     strict = os.environ.get("FRNN_CHECK", "0") not in ("", "0")
+    guard = _GuardedBuffers() if os.environ.get("FRNN_GUARD", "0") not in ("", "0") else None
+
+    def alloc(what, shape, stride, dtype, device, zero=False):
+        """A buffer the kernels write; between guard bands with FRNN_GUARD=1."""
+        if guard is not None:
+            return guard.empty(what, shape, stride, dtype, device, zero)
+        t = th.empty_strided(tuple(shape), tuple(stride), dtype=dtype, device=device)
+        return t.zero_() if zero else t
+
+    def alloc_like(what, like, device, dtype=None, zero=False):
+        m = th.empty_like(like, device="meta") if dtype is None else th.empty(like.shape, dtype=dtype, device="meta")
+        return alloc(what, m.shape, m.stride(), m.dtype, device, zero)
+
+    def check_guard(device):
+        """FRNN_GUARD=1: wait for the launch and look at the bands around everything it wrote."""
+        if guard is not None:
+            if not emulated:
+                th.cuda.synchronize(device)
+            guard.check()
 
     def check_before(device):
         """Raise if a kernel launched by an earlier call on this device reported
@@ -758,9 +821,14 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             device_status(device).check_now(th.cuda.current_stream(device).cuda_stream)
 
     def check_align(ts, flags, what):
+        """What the generated index arithmetic relies on: the alignment seen at compilation, and that the
+        last element the strides reach lies inside the tensor's storage."""
         for i, (t, f) in enumerate(zip(ts, flags)):
             assert (t.data_ptr() % 16 == 0) or not f, (
                 f"{what} #{i + 1} was 16-byte aligned at compilation but is not now")
+            reach = 1 + sum((n - 1) * s for n, s in zip(t.shape, t.stride()) if n > 1)
+            have = t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
+            assert t.numel() == 0 or reach <= have, f"{what} #{i + 1}: its strides reach past the end of its storage"
 
     # timing alternative tilings costs a few NVRTC compilations: only worth it for work of benchmark size
     no_tune = (_launcher is not None or not plan.tuning.autotune
@@ -838,11 +906,13 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         device = inputs_[0].device
         with _device_ctx(device):
             check_before(device)
-            outs = tuple(th.empty(p.B, p.T, p.H, p.M, dtype=d, device=device)
-                         for d in [o[2] for o in fw_meta[:nout]])
-            stT = tuple(th.empty_like(s) for s in state0)
-            store = tuple(th.empty(p.B, p.H, plan.nck, p.M, p.N, dtype=th.float32, device=device) for _ in state0)
-            aux = th.empty(len(plan.aux), p.B, p.H, p.T, p.M, dtype=th.float32, device=device)
+            cont = lambda *shape: (shape, lower._contig(shape))
+            outs = tuple(alloc(f"output #{j + 1}", *cont(p.B, p.T, p.H, p.M), o[2], device)
+                         for j, o in enumerate(fw_meta[:nout]))
+            stT = tuple(alloc_like(f"final state #{k + 1}", s, device) for k, s in enumerate(state0))
+            store = tuple(alloc(f"checkpoints of state #{k + 1}", *cont(p.B, p.H, plan.nck, p.M, p.N), th.float32, device)
+                          for k, _ in enumerate(state0))
+            aux = alloc("saved row sums", *cont(len(plan.aux), p.B, p.H, p.T, p.M), th.float32, device)
             ew = err_word(device)
             ptrs = [x.data_ptr() for x, u in zip(inputs_, fw_used[:nin]) if u]
             ptrs += [s.data_ptr() for s in state0] + [o.data_ptr() for o in outs] + [s.data_ptr() for s in stT]
@@ -851,6 +921,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
                 autotune_forward(ptrs, device)
             tuned["launch_fw"](ptrs, device)
             check_status(device, "forward")
+            check_guard(device)
         return (*outs, *stT, *store, aux)
 
     def backward(doutput, dstateT, inputs_, state_store, aux_):
@@ -863,13 +934,12 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
         with _device_ctx(device):
             check_before(device)
             dxs = []
-            for go, x in zip(plan.grads, inputs_):
+            for i, (go, x) in enumerate(zip(plan.grads, inputs_)):
                 if go.atomic:
-                    dxs.append(th.zeros(x.shape, dtype=th.float32, device=device))
+                    dxs.append(alloc_like(f"gradient of input #{i + 1}", x, device, dtype=th.float32, zero=True))
                 else:
-                    dxs.append(th.empty_like(x))
-            ds0 = tuple(th.empty_strided(m.shape, m.stride(), dtype=m.dtype, device=device) for m in
-                        (th.empty_like(s, device="meta") for s in st_meta))
+                    dxs.append(alloc_like(f"gradient of input #{i + 1}", x, device))
+            ds0 = tuple(alloc_like(f"gradient of initial state #{k + 1}", s, device) for k, s in enumerate(st_meta))
             ew = err_word(device)
             ptrs = [x.data_ptr() for x, u in zip(inputs_, bw_used[:nin]) if u]
             ptrs += [d.data_ptr() for d in doutput] + [d.data_ptr() for d in dstateT]
@@ -879,6 +949,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
                 autotune_backward(ptrs, device, dxs, ds0)
             tuned["launch_bw"](ptrs, device)
             check_status(device, "backward")
+            check_guard(device)
             for i, go in enumerate(plan.grads):
                 if go.atomic:
                     dxs[i] = dxs[i].to(inputs_[i].dtype)

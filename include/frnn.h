@@ -104,7 +104,10 @@ int frnn_tensor_map_encode(void* out_map, const void* base, unsigned elt_bytes, 
  * Kernel error word.  Every device-side wait of the generated kernels is
  * time-bounded; a kernel whose wait ran out writes a non-zero code into the
  * `int` error word it was given as its last pointer parameter and returns
- * early, so its outputs are not valid.  (The reference has no counterpart: its
+ * early, so its outputs are not valid.  A kernel compiled with -DFRNN_BOUNDS
+ * (the checked build: every access is tested against the byte extents the
+ * generator registered for the kernel's buffers) writes code 64 when it
+ * refused an access outside them.  (The reference has no counterpart: its
  * stubs check nothing, flex_rnn/to_cuda.py:245-252.)  The word is sticky until
  * one of the calls below clears it.  It may live in device memory or in pinned
  * host memory, which the device writes directly under unified addressing; the
