@@ -276,6 +276,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     for i, x in enumerate(state):
         assert list(x.shape) == [B, H, M, N], f"shape {list(x.shape)} of argument #{i + 1 + len(inputs)} != {[B, H, M, N]}"
         assert x.dtype in _IO_DTYPES, f"unsupported dtype {x.dtype} of argument #{i + 1 + len(inputs)}"
+    assert state[0].shape[-2] >= 1 and state[0].shape[-1] >= 1, f"a state needs at least one row and one column, got {list(state[0].shape)}"
     nin, nst = len(inputs), len(state)
 
     # output arity and dtypes: run the step on meta tensors of the original dtypes
@@ -743,6 +744,44 @@ def _build_row_padded(step, inputs, state, Mp, dryrun, tuning, _launcher):
     return forward, backward, fw_meta, bw_meta
 
 
+def _build_empty(plan: Plan, fw_meta, bw_meta, inputs, state):
+    """Host closures for a problem without a single timestep, batch row or head:
+    there is nothing to scan and no kernel to launch (a grid or a loop of extent
+    zero is not something the generated kernels are built for).  Outputs are
+    empty, the final state is the initial state (or empty), gradients of the
+    inputs are zero and the gradient of the initial state is the upstream
+    gradient of the final state."""
+    in_meta = tuple(th.empty_strided(x.shape, x.stride(), dtype=x.dtype, device="meta") for x in inputs)
+    st_meta = tuple(th.empty_strided(x.shape, x.stride(), dtype=x.dtype, device="meta") for x in state)
+
+    def like(meta, device):
+        shape, stride, dtype = meta
+        return th.empty_strided(tuple(shape), tuple(stride), dtype=dtype, device=device).zero_()
+
+    def forward(inputs_, state0):
+        verify_meta(inputs_, in_meta, "input Tensor metadata doesn't match compilation\n")
+        verify_meta(state0, st_meta, "initial state Tensor metadata doesn't match compilation\n")
+        device = state0[0].device
+        res = [like(m, device) for m in fw_meta]
+        for k, s in enumerate(state0):
+            res[plan.n_out + k].copy_(s)
+        return tuple(res)
+
+    def backward(doutput, dstateT, inputs_, state_store, aux_):
+        device = dstateT[0].device
+        nin = len(in_meta)
+        dxs = tuple(like(m, device) for m in bw_meta[:nin])
+        ds0 = tuple(like(m, device).copy_(d) for m, d in zip(bw_meta[nin:], dstateT))
+        return dxs, ds0
+
+    forward.plan = plan                      # type: ignore[attr-defined]
+    forward.sources = ()                     # type: ignore[attr-defined]
+    forward.launchers = ()                   # type: ignore[attr-defined]
+    forward.kernel_status = lambda device=None: 0   # type: ignore[attr-defined]
+    forward.tuned = {"fw_choice": 0, "bw_choice": 0, "fw_log": [], "bw_log": []}   # type: ignore[attr-defined]
+    return forward, backward
+
+
 def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = None, _launcher=None):
     """See the module docstring.  With ``dryrun`` nothing touches CUDA.
 
@@ -764,6 +803,8 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
     if dev.type != "cuda" and _launcher is None:
         raise RuntimeError("flex_rnn_b200 runs on CUDA devices only (there is no CPU path); "
                            "use the .naive method for a CPU evaluation of the step function")
+    if 0 in (plan.problem.B, plan.problem.T, plan.problem.H):
+        return (*_build_empty(plan, fw_meta, bw_meta, inputs, state), fw_meta, bw_meta)
     fw_src, bw_src = generate(plan)
     tu0 = plan.tuning
     forced_fw, forced_bw = tu0.fw_variant >= 0, tu0.bw_variant >= 0

@@ -224,3 +224,24 @@ def test_examples_cli_and_benchmark(capsys):
     op = flex_rnn_b200.jit(O.mamba2)
     ms = flex_rnn_b200.benchmark(op, [x.to(DEV) for x in xs], warmup=2, rep=5, verbose=False)
     assert 0.0 < ms < 1e3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,H", [(2, 0, 3), (0, 5, 3), (2, 5, 0)])
+def test_empty_problems_launch_nothing(B, T, H):
+    """No timestep, no batch row or no head: outputs are empty, the final state
+    is the initial state, input gradients are zero (empty) and the gradient of
+    the initial state is the upstream gradient of the final state; through the
+    public API and autograd, without a kernel launch."""
+    M, N = 64, 64
+    op = flex_rnn_b200.jit(O.STEPS["gated_delta_rule"])
+    g = torch.Generator().manual_seed(0)
+    mk = lambda *s: torch.randn(*s, generator=g).to("cuda:0").requires_grad_()
+    q, k, v, gate, beta, S = mk(B, T, H, 1, N), mk(B, T, H, 1, N), mk(B, T, H, M, 1), mk(B, T, H, 1, 1), mk(B, T, H, 1, 1), mk(B, H, M, N)
+    y, ST = op(q, k, v, gate, beta, S)
+    assert y.shape == (B, T, H, M) and ST.shape == S.shape and torch.equal(ST, S)
+    dS = torch.randn(B, H, M, N, generator=g).to("cuda:0")
+    grads = torch.autograd.grad([y, ST], [q, k, v, gate, beta, S], [torch.zeros_like(y), dS])
+    assert all(gr.shape == x.shape and not gr.any() for gr, x in zip(grads[:-1], [q, k, v, gate, beta]))
+    assert torch.equal(grads[-1], dS)
+    assert op.forward_func.sources == () and op.forward_func.kernel_status("cuda:0") == 0

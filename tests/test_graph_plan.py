@@ -245,3 +245,25 @@ def test_product_reassociation():
                                           Node("k", "add", ["m1", "m2"], MN)], ["k"],
                    {"T": MN, "s": S11, "y": M1, "m1": MN, "m2": MN, "k": MN})
     assert [n.name for n in g2.simplified_products().nodes] == ["m1", "m2", "k"]
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 0, 2), (0, 4, 2), (2, 3, 0)])
+def test_empty_problems_build_no_kernel(B, T, H):
+    """A problem without a timestep, a batch row or a head gets host closures that launch nothing (the launcher
+    seam given here would raise if it were ever constructed)."""
+    import torch
+    from flex_rnn_b200.twopass import build_twopass
+    from oracle import naive_oracle as O
+
+    def never(ks):
+        raise AssertionError("a kernel was built for an empty problem")
+
+    q, k = torch.randn(B, T, H, 1, 16), torch.randn(B, T, H, 1, 16)
+    v, beta, S = torch.randn(B, T, H, 16, 1), torch.rand(B, T, H, 1, 1), torch.randn(B, H, 16, 16)
+    fwd, bwd, fm, bm = build_twopass(O.STEPS["delta_rule"], (q, k, v, beta), (S,), _launcher=never)
+    y, ST, store, aux = fwd((q, k, v, beta), (S,))
+    assert tuple(y.shape) == (B, T, H, 16) and torch.equal(ST, S)
+    assert [tuple(m[0]) for m in fm] == [tuple(t.shape) for t in (y, ST, store, aux)]
+    dS = torch.randn(B, H, 16, 16)
+    dx, ds0 = bwd((torch.zeros_like(y),), (dS,), (q, k, v, beta), (store,), (aux,))
+    assert [tuple(d.shape) for d in dx] == [tuple(x.shape) for x in (q, k, v, beta)] and torch.equal(ds0[0], dS)
