@@ -262,6 +262,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
               tuning: Optional[Tuning] = None) -> Tuple[Plan, tuple, tuple]:
     inputs, state = tuple(inputs), tuple(state)
     assert len(state) >= 1, "a step function needs at least one state"
+    assert not any(0 in s.shape[-2:] for s in state), f"a state needs at least one row and one column, got {list(state[0].shape)}"
     B, T, H = [max(i.shape[j] for i in inputs) for j in range(3)] if inputs else (state[0].shape[0], 1, state[0].shape[1])
     M = max(i.shape[-2] for i in inputs + state)
     N = max(i.shape[-1] for i in inputs + state)
@@ -276,7 +277,6 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     for i, x in enumerate(state):
         assert list(x.shape) == [B, H, M, N], f"shape {list(x.shape)} of argument #{i + 1 + len(inputs)} != {[B, H, M, N]}"
         assert x.dtype in _IO_DTYPES, f"unsupported dtype {x.dtype} of argument #{i + 1 + len(inputs)}"
-    assert state[0].shape[-2] >= 1 and state[0].shape[-1] >= 1, f"a state needs at least one row and one column, got {list(state[0].shape)}"
     nin, nst = len(inputs), len(state)
 
     # output arity and dtypes: run the step on meta tensors of the original dtypes
@@ -668,6 +668,8 @@ def _padded_rows(inputs, state) -> Optional[int]:
     of two dividing N), so M x lanes must be a multiple of 32."""
     M = max(i.shape[-2] for i in tuple(inputs) + tuple(state))
     N = max(i.shape[-1] for i in tuple(inputs) + tuple(state))
+    if any(0 in s.shape[-2:] for s in state):
+        return None                  # refused with a message by make_plan
     lanes = max(L for L in (1, 2, 4, 8, 16, 32) if N % L == 0)
     k = 1
     while (M * k * lanes) % 32:
