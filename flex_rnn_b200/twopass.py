@@ -508,7 +508,12 @@ def generate_forward(plan: Plan, tile: Optional[lower.Tile] = None, pack: Option
                           step_unroll=unroll or tu.fw_unroll, pack2=pack2, col_major=bool(tu.col_major),
                           max_acc=tu.fw_acc)
         ncta = fw.grid[0] * fw.grid[1] * fw.grid[2]
-        per_sm = min(max(1, -(-ncta // getattr(plan, "n_sm", B200_SMS))), 2048 // fw.block, 32)
+        # CTAs an SM will hold at once: as many as there are per SM, but no more than the register file admits
+        # (the state tiles plus about 96 registers of vectors and addresses per thread, unless the launch bounds
+        # ask for more CTAs and accept the spills)
+        by_regs = 65536 // (fw.block * min(255, tile.R * tile.C * plan.n_st + 96))
+        per_sm = min(max(1, -(-ncta // getattr(plan, "n_sm", B200_SMS))), 2048 // fw.block, 32,
+                     max(1, by_regs, tu.fw_min_blocks))
         if stage <= 4 or fw.smem_bytes * per_sm <= 200 * 1024:
             break
         stage //= 2
