@@ -564,14 +564,21 @@ def forward_variants(plan: Plan) -> List[dict]:
 def backward_variants(plan: Plan) -> List[dict]:
     """Keyword arguments of ``generate_backward`` for every backward kernel the
     autotuner may pick; member 0 is the planned kernel."""
-    return [dict(tile=t) for t in backward_tile_candidates(plan)]
+    out = [dict(tile=t) for t in backward_tile_candidates(plan)]
+    # the planned tile with the other kind of arithmetic (scalar FMAs measured 9 % faster than packed ones on
+    # Mamba-2's 64x128 state, 8-24 % slower on the 128x128 workloads)
+    out.append(dict(tile=plan.bw_tile, pack=not bool(plan.tuning.pack2 & 1)))
+    return out
 
 
-def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional[lower.KernelSource]:
+def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None,
+                      pack: Optional[bool] = None) -> Optional[lower.KernelSource]:
     """Emit the backward kernel.  For a ``tile`` other than the planned one the
     checkpoint interval and slot count stay what the forward was built for and
-    only the flush parameters are re-fitted; None if it does not fit."""
+    only the flush parameters are re-fitted; None if it does not fit.  ``pack``
+    switches the packed two-column arithmetic on or off (default: the plan's)."""
     p, tu = plan.problem, plan.tuning
+    pack2 = bool(tu.pack2 & 1) if pack is None else bool(pack)
     sg, kflush, bufs = plan.bw_choice
     cands = [(kflush, bufs)]
     if tile is not None and tile is not plan.bw_tile:
@@ -584,7 +591,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None) -> Optional
         bw = emit_backward(p, plan.g_re, plan.g_bw, plan.aux, plan.n_out, plan.grads, plan.dy_names,   # type: ignore[attr-defined]
                            plan.dnext_names, tile or plan.bw_tile, sg, tu.nslots, tu.use_tma, prelude(),  # type: ignore[attr-defined]
                            kflush=kf, ring_bufs=nb, reverse=plan.reverse, step_unroll=tu.bw_unroll,
-                           min_blocks=max(1, tu.bw_min_blocks), pack2=bool(tu.pack2 & 1), col_major=bool(tu.col_major),
+                           min_blocks=max(1, tu.bw_min_blocks), pack2=pack2, col_major=bool(tu.col_major),
                            helper_warps=tu.bw_helper, max_acc=tu.bw_acc, tmem_slots=tu.bw_tmem_slots,
                            post_split=plan.post_split, unroll_segment=int(tu.bw_unroll_seg))
         if bw.smem_bytes <= _bw_smem_limit(tu):
@@ -925,7 +932,7 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
                 ms = timed(launcher, trial, device)
             except (lower.LoweringError, RuntimeError):
                 continue
-            log.append((k, ks.info["tile"], round(ms, 4)))
+            log.append((k, ks.info["tile"], bool(ks.info["packed"]), round(ms, 4)))
             if best is None or ms < best[0]:
                 best = (ms, launcher, ks, k)
         if best is not None:
