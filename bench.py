@@ -662,7 +662,8 @@ def run_ours(args, rank, world, local):
             base = runs[-1][0]
             mean_dt = sum(dt for _, dt in runs) / len(runs)
             base["value"] = base["value"] * runs[-1][1] / mean_dt
-            base["sample"] += f"; mean of 3 passes after one cold pass ({mean_dt:.2f} s each)"
+            base["sample"] = base["sample"].replace(f", {runs[-1][1]:.2f} s, scaled",
+                                                    f", {mean_dt:.2f} s per pass (mean of 3 after one cold pass), scaled")
             line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     if world > 1:
