@@ -99,6 +99,8 @@ class Tuning:
     bw_min_blocks: int = 0   # backward CTAs per SM the kernel is built for (2: half the registers and shared memory
                              # each); 0 = two when the planned tile gives CTAs of at most 128 threads, else one
     pack2: int = 1           # packed fp32x2 arithmetic (two columns per instruction): bit 0 backward, bit 1 forward
+    bw_pack_small: int = 0   # packed arithmetic also in backward kernels built for two CTAs of four compute warps per
+                             # SM (a 64x128 state): scalar FMAs measured 9 % faster there, issue slots are not short
     autotune_min_work: int = 1 << 28   # B*T*H*M*N below which the planned tiles are used untimed
     autotune: int = 1        # time alternative forward tiles on the first call and keep the fastest
     fw_variant: int = -1     # >= 0: use this member of forward_variants(plan) untimed (tests, reproducible runs)
@@ -567,8 +569,15 @@ def backward_variants(plan: Plan) -> List[dict]:
     out = [dict(tile=t) for t in backward_tile_candidates(plan)]
     # the planned tile with the other kind of arithmetic (scalar FMAs measured 9 % faster than packed ones on
     # Mamba-2's 64x128 state, 8-24 % slower on the 128x128 workloads)
-    out.append(dict(tile=plan.bw_tile, pack=not bool(plan.tuning.pack2 & 1)))
+    out.append(dict(tile=plan.bw_tile, pack=not _bw_packed(plan, plan.bw_tile)))
     return out
+
+
+def _bw_packed(plan: Plan, tile: lower.Tile) -> bool:
+    """Whether a backward kernel with this tile uses packed two-column arithmetic by default."""
+    tu = plan.tuning
+    two_small_ctas = tile.NT <= 128 and tu.bw_min_blocks >= 2
+    return bool(tu.pack2 & 1) and (not two_small_ctas or bool(tu.bw_pack_small))
 
 
 def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None,
@@ -578,7 +587,7 @@ def generate_backward(plan: Plan, tile: Optional[lower.Tile] = None,
     only the flush parameters are re-fitted; None if it does not fit.  ``pack``
     switches the packed two-column arithmetic on or off (default: the plan's)."""
     p, tu = plan.problem, plan.tuning
-    pack2 = bool(tu.pack2 & 1) if pack is None else bool(pack)
+    pack2 = _bw_packed(plan, tile or plan.bw_tile) if pack is None else bool(pack)
     sg, kflush, bufs = plan.bw_choice
     cands = [(kflush, bufs)]
     if tile is not None and tile is not plan.bw_tile:
