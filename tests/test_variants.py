@@ -1,8 +1,9 @@
 """Every kernel variant the autotuner may pick, each checked on its own.
 
 On the first call of a benchmark-sized problem the planner times alternative
-forward kernels (tilings, packed or scalar arithmetic, one fully unrolled chunk
-per checkpoint interval) and backward tilings, and keeps the fastest; which one
+forward kernels (tilings, packed or scalar arithmetic, longer staged chunks, one
+fully unrolled chunk per checkpoint interval) and backward kernels (tilings,
+the other kind of arithmetic), and keeps the fastest; which one
 wins depends on the GPU's state at that moment.  So parity must hold for every
 member of ``forward_variants`` / ``backward_variants``, not only for the
 planned kernel that small test cases run.  Here each member is forced through
