@@ -149,3 +149,15 @@ def test_expanded_input(dim):
     dx, ds0 = bwd((dy,), (dS,), tuple(xs[:-1]), (store,), (aux,))
     dense = [x.contiguous() for x in xs]
     check("delta_rule", dense, dy, dS, (y, ST, list(dx) + list(ds0)), 1e-5, 1e-5)
+
+
+def test_mixed_io_dtypes():
+    """bf16, fp16, fp64 and fp32 tensors in one call: the output takes the dtype
+    torch's promotion gives the step (fp64 here), the final state its initial
+    state's, each gradient its input's; arithmetic in fp32."""
+    xs, dy, dS = O.make_case("delta_rule", 1, 9, 2, 16, 16, torch.float32)
+    dts = [torch.bfloat16, torch.float16, torch.float64, torch.float32, torch.float32]
+    xs = [x.to(d) for x, d in zip(xs, dts)]
+    y, ST, grads, _ = run_emu("delta_rule", xs, dy, dS, SMALL)
+    assert y.dtype == torch.float64 and ST.dtype == torch.float32
+    check("delta_rule", xs, dy, dS, (y, ST, grads), 1e-5, 1e-2)

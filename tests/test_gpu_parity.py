@@ -245,3 +245,22 @@ def test_empty_problems_launch_nothing(B, T, H):
     assert all(gr.shape == x.shape and not gr.any() for gr, x in zip(grads[:-1], [q, k, v, gate, beta]))
     assert torch.equal(grads[-1], dS)
     assert op.forward_func.sources == () and op.forward_func.kernel_status("cuda:0") == 0
+
+
+@pytest.mark.gpu
+def test_mixed_and_fp64_io_dtypes():
+    """Every tensor in its own I/O dtype (bf16, fp16, fp32 and fp64 in one call): the
+    output takes the dtype torch's promotion gives the step, each gradient its
+    input's, the arithmetic stays fp32 (the reference's contract, twopass.py:54-58,
+    74-76, 175-180 of the reference project)."""
+    B, T, H, M, N = 2, 37, 2, 64, 128
+    xs, dy, dS = O.make_case("delta_rule", B, T, H, M, N, torch.float32)
+    dts = [torch.bfloat16, torch.float16, torch.float64, torch.float32, torch.float32]     # q, k, v, beta, S
+    xs = [x.to(d) for x, d in zip(xs, dts)]
+    y, ST, grads, _ = run_gpu("delta_rule", xs, dy, dS)
+    ry, rST, rgx, rgs = O.fwd_bwd(O.STEPS["delta_rule"], xs[:-1], xs[-1:], [dy], [dS], dtype=torch.float64)
+    assert y.dtype == torch.float64 and ST.dtype == torch.float32          # v is fp64: the row sums promote to it
+    assert O.rel_err(y, ry[0]) < 1e-5 and O.rel_err(ST, rST[0]) < 1e-5
+    for g, r, x in zip(grads, rgx + rgs, xs):
+        assert g.dtype == x.dtype and g.shape == x.shape
+        assert O.rel_err(g, r) < (1e-2 if x.dtype in (torch.bfloat16, torch.float16) else 1e-5)
