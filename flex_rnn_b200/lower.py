@@ -1434,7 +1434,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     kb = KernelBuilder(p, tile, D, use_tma)
     w, t = kb.w, tile
     if t.MB != p.M:
-        raise LoweringError("the backward kernel needs all rows of a head in one CTA")
+        # Rows split over several CTAs (a state too large for the registers of one SM): rows are independent
+        # recurrences, only the gradients summed over rows couple them, and those must then be accumulated
+        # across CTAs with atomic adds into fp32 (the planner marks them ``atomic``).
+        for go in grads:
+            if go.cls in (N1, S11) and not go.atomic:
+                raise LoweringError("rows split over CTAs need atomically accumulated column gradients")
     ws = helper_warps > 0
     NCT = t.NT
     # Register file: the hardware allots registers to a CTA as if its thread count were rounded up to whole
@@ -1534,7 +1539,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         tm_cols *= 2
     if tm and tm_cols > 512 // max(1, min_blocks):
         raise LoweringError("the segment bases do not fit the Tensor Memory of one SM")
-    slot_elems = p.M * p.N
+    slot_elems = t.MB * p.N           # rows of this CTA
     slot_bytes = slot_elems * 4
     ck_tma = (not rev) and use_tma and slot_bytes % 16 == 0
     BAR_BYTES = 128
@@ -1547,7 +1552,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
     # per-row gradients written every step (dv ...) are parked next to the ring and stored at flush time
     row_st = [go for go in grads if go.cls == M1 and not go.over_t and not go.atomic] if redw else []
     off_ob = off_ring + ring_bytes
-    ob_bytes = ring_bufs * kflush * len(row_st) * p.M * 4
+    ob_bytes = ring_bufs * kflush * len(row_st) * t.MB * 4
     smem_bytes = off_ob + ob_bytes
     # mbarriers: 0 staged inputs, 2 checkpoint copy; with helper warps 3,4 work buffer full, 5,6 work buffer empty,
     # 7,8 ring half full, 9,10 ring half empty
@@ -1667,9 +1672,9 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         gradients; run by the threads ``ftid`` in [0, FT)."""
         w(f"const float* rr = ring + ({half}) * {kflush * step_floats};")
         for vi, go in enumerate(row_st):
-            kb.emit_obuf_flush(f"(obuf + ({half}) * {kflush * len(row_st) * p.M})", rcnt, vi, len(row_st), go.spec.dt,
+            kb.emit_obuf_flush(f"(obuf + ({half}) * {kflush * len(row_st) * t.MB})", rcnt, vi, len(row_st), go.spec.dt,
                                f"dx{go.index}",
-                               lambda sx, go=go: _elem_off(go.spec, [(0, "b"), (1, f"({rt_first}) - {sx}"), (2, "h")]),
+                               lambda sx, go=go: _elem_off(go.spec, [(0, "b"), (1, f"({rt_first}) - {sx}"), (2, "h"), (3, "m0")]),
                                go.spec.st(3),
                                go.spec.aligned16 and all((go.spec.st(d) * ELT[go.spec.dt]) % 16 == 0 for d in (0, 1, 2)),
                                tidv=ftid, nthr=FT)
@@ -1824,12 +1829,12 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
             w("frnn_async_proxy_fence();")
             w(f"frnn_mbar_expect_tx(&full[{B_CK}], {ns * slot_bytes}u);")
             for k in range(ns):
-                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
+                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr), (3, "m0")])
                 w(f"frnn_bulk_g2s_c(slots + ((long)({physexpr}) * {ns} + {k}) * {slot_elems}, ck{k} + {base}, {slot_bytes}u, &full[{B_CK}]);")
             w.close()
         else:
             for k in range(ns):
-                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr)])
+                base = _elem_off(ckspec, [(0, "b"), (1, "h"), (2, kexpr), (3, "m0")])
                 w(f"for (int e = tid; e < {slot_elems}; e += {NCT}) "
                   f"slots[((long)({physexpr}) * {ns} + {k}) * {slot_elems} + e] = ck{k}[{base} + e];")
 
@@ -2273,7 +2278,7 @@ def emit_backward(p: Problem, g_re: StepGraph, g_bw: StepGraph, aux_names: List[
         w(f"frnn_tmem_dealloc(tm_base, {tm_cols}u);")
         w.close()
     w.close()
-    return KernelSource(kname, w.text().replace("@SMEM_BYTES@", str(smem_bytes)), (1, p.H, p.B), NCT + HT, smem_bytes,
+    return KernelSource(kname, w.text().replace("@SMEM_BYTES@", str(smem_bytes)), (p.M // t.MB, p.H, p.B), NCT + HT, smem_bytes,
                         kb.params, kb.param_decl,
                         {"stage_bytes": stage_bytes, "wk_bytes": kb.wk_bytes, "slot_bytes": slot_bytes if nphys else 0,
                          "ring_bytes": ring_bytes, "tma_items": len(kb.tma_items), "plain_items": len(kb.plain_items),

@@ -83,6 +83,7 @@ class Tuning:
     fw_min_blocks: int = 1
     bw_r: int = 8            # backward tile
     bw_c: int = 8
+    bw_mb: int = 0           # state rows per backward CTA (0 = all rows of a head, fewer only when they do not fit one CTA)
     seg: int = 4             # generic backward: steps per segment, segments (slots) per checkpoint chunk
     nslots: int = 2
     kflush: int = 8          # steps of gradient partials reduced together (lowered until shared memory fits)
@@ -338,12 +339,35 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         fr, fc = (fr // 2, fc) if fr >= 4 else (fr, max(1, fc // 2))
     while br * bc * bw_tiles > 160 and br * bc > 4:
         br, bc = (br // 2, bc) if br >= bc else (br, max(1, bc // 2))
-    fw_tile = choose_tile(M, N, fr, fc, tu.fw_mb)
+    def fitted_tile(want_r, want_c, want_mb, n_tiles, extra_threads):
+        """The tile nearest to the wish whose CTA fits an SM's register file: a row needs at least N/32 columns
+        per thread, so wide states get fewer rows per thread, and a CTA whose threads' tiles (plus about 96
+        working registers each) exceed the 64 K registers gives rows to further CTAs.  Rows are independent
+        recurrences; only the gradients summed over rows couple them (accumulated across CTAs, see below)."""
+        t = choose_tile(M, N, want_r, want_c, want_mb)
+        while t.R * t.C * n_tiles > 160 and t.R > 1:
+            t = choose_tile(M, N, t.R // 2, want_c, want_mb)
+        mb = t.MB
+        while mb % 2 == 0 and mb // 2 >= t.R:
+            limit = min(1024 - extra_threads, 65536 // (t.R * t.C * n_tiles + 96) // 32 * 32)
+            if t.NT <= max(32, limit):
+                break
+            try:
+                t2 = choose_tile(M, N, t.R, want_c, mb // 2)
+            except lower.LoweringError:
+                break
+            if t2.MB >= mb:
+                break
+            mb, t = t2.MB, t2
+        return t
+
+    fw_tile = fitted_tile(fr, fc, tu.fw_mb, fw_tiles, 0)
     if fw_tile.NT < 128 and fc >= 32:
         # a forward CTA of fewer than four warps leaves schedulers with a single warp: halve the columns per
         # thread instead (Mamba-2's 64x128 state: R4xC16, 128 threads, measured 4 % faster than R4xC32)
-        fw_tile = choose_tile(M, N, fr, fc // 2, tu.fw_mb)
-    bw_tile = choose_tile(M, N, br, bc, None)
+        fw_tile = fitted_tile(fr, fc // 2, tu.fw_mb, fw_tiles, 0)
+    bw_tile = fitted_tile(br, bc, tu.bw_mb or None, bw_tiles, 128 if tu.bw_helper else 0)
+    rows_split = bw_tile.MB < M
     # additive state update S' = S +/- X with X free of the state (given the saved row sums):
     # the backward can step the state backwards instead of recomputing it from checkpoints
     reverse = None
@@ -374,7 +398,7 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     grads: List[GradOut] = []
     for i, x in enumerate(inputs):
         cls = in_cls[i]
-        atomic = list(x.shape[:3]) != [B, T, H]
+        atomic = list(x.shape[:3]) != [B, T, H] or (rows_split and cls in (N1, S11))
         over_t = x.shape[1] == 1 and T > 1
         gm = dx_meta[i]
         if atomic:
@@ -614,7 +638,7 @@ def backward_tile_candidates(plan: Plan) -> List[lower.Tile]:
     n_tiles = 2 * plan.n_st + 2 * sum(1 for g in plan.grads if g.cls == MN)
     for r, c in ((8, 8), (4, 8), (4, 16), (8, 4)):
         try:
-            t = choose_tile(p.M, p.N, r, c, None)
+            t = choose_tile(p.M, p.N, r, c, plan.bw_tile.MB if plan.bw_tile.MB < p.M else None)
         except lower.LoweringError:
             continue
         if (t.R, t.C) not in seen and t.R * t.C * n_tiles <= 160:
@@ -1022,8 +1046,8 @@ def build_twopass(step, inputs, state, dryrun=False, tuning: Optional[Tuning] = 
             check_status(device, "backward")
             check_guard(device)
             for i, go in enumerate(plan.grads):
-                if go.atomic:
-                    dxs[i] = dxs[i].to(inputs_[i].dtype)
+                if go.atomic:          # accumulated in fp32: now in the input's dtype and layout
+                    dxs[i] = th.empty_like(inputs_[i]).copy_(dxs[i])
         return tuple(dxs), ds0
 
     def kernel_status(device=None) -> int:

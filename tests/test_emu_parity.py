@@ -161,3 +161,17 @@ def test_mixed_io_dtypes():
     y, ST, grads, _ = run_emu("delta_rule", xs, dy, dS, SMALL)
     assert y.dtype == torch.float64 and ST.dtype == torch.float32
     check("delta_rule", xs, dy, dS, (y, ST, grads), 1e-5, 1e-2)
+
+
+@pytest.mark.parametrize("op", list(W.STEPS))
+def test_backward_rows_split_over_ctas(op):
+    """A state too large for one CTA has its rows split over several backward
+    CTAs; the gradients summed over rows (per-column and per-head ones) are then
+    accumulated across CTAs in fp32.  Forced here on a 16x16 state (8 rows per
+    CTA), both backward modes, ragged T."""
+    import dataclasses
+    xs, dy, dS = O.make_case(op, 2, 9, 2, 16, 16, torch.float32)
+    y, ST, grads, fwd = run_emu(op, xs, dy, dS, dataclasses.replace(SMALL, bw_mb=8))
+    assert fwd.sources[1].grid[0] == 2 and fwd.sources[1].info["tile"][2] == 8
+    assert all(go.atomic for go in fwd.plan.grads if go.cls != (1, 0))
+    check(op, xs, dy, dS, (y, ST, grads), 1e-5, 1e-5)

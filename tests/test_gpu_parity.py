@@ -264,3 +264,21 @@ def test_mixed_and_fp64_io_dtypes():
     for g, r, x in zip(grads, rgx + rgs, xs):
         assert g.dtype == x.dtype and g.shape == x.shape
         assert O.rel_err(g, r) < (1e-2 if x.dtype in (torch.bfloat16, torch.float16) else 1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op_name,M,N", [("delta_rule", 256, 256), ("gated_delta_rule", 256, 256), ("rwkv7", 256, 256),
+                                         ("mamba2", 512, 128), ("delta_rule", 1024, 64)])
+def test_states_larger_than_one_cta(op_name, M, N):
+    """65 536 state elements per head: S and dS do not fit the registers of one SM,
+    so the backward splits the rows of a head over several CTAs (the forward
+    already tiles rows) and accumulates the per-column gradients across them."""
+    B, T, H = 1, 20, 2
+    xs, dy, dS = O.make_case(op_name, B, T, H, M, N, torch.float32)
+    y, ST, grads, op = run_gpu(op_name, xs, dy, dS)
+    assert op.forward_func.sources[1].grid[0] > 1
+    ry, rST, rgx, rgs = O.fwd_bwd(O.STEPS[op_name], xs[:-1], xs[-1:], [dy], [dS], dtype=torch.float64)
+    assert O.rel_err(y, ry[0]) < 1e-5 and O.rel_err(ST, rST[0]) < 1e-5
+    for g, r, x in zip(grads, rgx + rgs, xs):
+        assert g.shape == x.shape and g.dtype == x.dtype
+        assert O.rel_err(g, r) < 1e-5, (op_name, O.rel_err(g, r))
