@@ -395,17 +395,25 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
     prob = Problem(B, T, H, M, N, [_spec(x) for x in inputs], list(in_names), [_spec(s) for s in state],
                    list(st_names), [_DT[d] for d in out_dtypes], len(aux))
     dx_meta = tuple(th.empty_like(x, device="meta") for x in inputs)
-    grads: List[GradOut] = []
-    for i, x in enumerate(inputs):
-        cls = in_cls[i]
-        atomic = list(x.shape[:3]) != [B, T, H] or (rows_split and cls in (N1, S11))
-        over_t = x.shape[1] == 1 and T > 1
-        gm = dx_meta[i]
-        if atomic:
-            spec = TensorSpec(tuple(gm.shape), tuple(th.empty(gm.shape, device="meta").stride()), DT_F32, True)
-        else:
-            spec = TensorSpec(tuple(gm.shape), tuple(gm.stride()), _DT[gm.dtype], True)
-        grads.append(GradOut(i, cls, spec, dx_names[i], over_t, atomic))
+
+    def make_grads(rows_split: bool) -> List[GradOut]:
+        """Where each input's gradient goes: its own dtype and layout, or fp32 with atomic accumulation when
+        several CTAs or timesteps add to the same element (inputs broadcast over B, T or H; gradients summed
+        over rows when the rows of a head are split over CTAs)."""
+        out = []
+        for i, x in enumerate(inputs):
+            cls = in_cls[i]
+            atomic = list(x.shape[:3]) != [B, T, H] or (rows_split and cls in (N1, S11))
+            over_t = x.shape[1] == 1 and T > 1
+            gm = dx_meta[i]
+            if atomic:
+                spec = TensorSpec(tuple(gm.shape), tuple(th.empty(gm.shape, device="meta").stride()), DT_F32, True)
+            else:
+                spec = TensorSpec(tuple(gm.shape), tuple(gm.stride()), _DT[gm.dtype], True)
+            out.append(GradOut(i, cls, spec, dx_names[i], over_t, atomic))
+        return out
+
+    grads = make_grads(rows_split)
 
     # pick the backward's staging / flush parameters that fit shared memory
     choice = None
@@ -483,7 +491,15 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         if auto_blocks and tu.bw_min_blocks > 1:
             tu.bw_min_blocks = 1          # half an SM's shared memory is not enough: one CTA per SM after all
             continue
-        break
+        # fewer rows per CTA: smaller slots and fewer row groups in the ring of gradient partials
+        try:
+            smaller = choose_tile(M, N, bw_tile.R, bw_tile.C, bw_tile.MB // 2) if bw_tile.MB % 2 == 0 else None
+        except lower.LoweringError:
+            smaller = None
+        if smaller is None or smaller.MB >= bw_tile.MB or smaller.NT < 32:
+            break
+        bw_tile = smaller
+        grads = make_grads(True)
     if reverse is not None and choice is not None and tu.bw_helper:
         reverse.resync = max(1, tu.rev_ckpt // choice[0])
     if choice is None:

@@ -268,7 +268,8 @@ def test_mixed_and_fp64_io_dtypes():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("op_name,M,N", [("delta_rule", 256, 256), ("gated_delta_rule", 256, 256), ("rwkv7", 256, 256),
-                                         ("mamba2", 512, 128), ("delta_rule", 1024, 64)])
+                                         ("mamba2", 512, 128), ("delta_rule", 1024, 64), ("rwkv7", 128, 512),
+                                         ("gated_delta_rule", 64, 1024)])
 def test_states_larger_than_one_cta(op_name, M, N):
     """65 536 state elements per head: S and dS do not fit the registers of one SM,
     so the backward splits the rows of a head over several CTAs (the forward
