@@ -346,7 +346,10 @@ def make_plan(step: Callable, inputs: Sequence[th.Tensor], state: Sequence[th.Te
         recurrences; only the gradients summed over rows couple them (accumulated across CTAs, see below)."""
         t = choose_tile(M, N, want_r, want_c, want_mb)
         while t.R * t.C * n_tiles > 160 and t.R > 1:
-            t = choose_tile(M, N, t.R // 2, want_c, want_mb)
+            t2 = choose_tile(M, N, t.R // 2, want_c, want_mb)
+            if t2.R >= t.R:          # fewer rows per thread would need more than 1024 threads at this row count
+                break
+            t = t2
         mb = t.MB
         while mb % 2 == 0 and mb // 2 >= t.R:
             limit = min(1024 - extra_threads, 65536 // (t.R * t.C * n_tiles + 96) // 32 * 32)
