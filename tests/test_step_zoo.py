@@ -94,15 +94,34 @@ def test_emulated_one_row_or_column_state(M, N):
             assert a.shape == b.shape and O.rel_err(a, b) < 1e-5
 
 
+LARGE = [("s4d", 256, 128), ("mamba", 256, 256), ("rwkv4", 8192, 1), ("rwkv6", 256, 256)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("op,M,N", LARGE, ids=[c[0] for c in LARGE])
+def test_gpu_states_larger_than_one_cta(op, M, N):
+    """Rows of a head split over several CTAs in both kernels: two states plus four
+    matrix inputs with their gradients (S4D), a matrix input's gradient across the
+    split (Mamba), three one-column states of 8192 rows (RWKV-4), a time-invariant
+    row input whose gradient sums over the split rows (RWKV-6)."""
+    test_gpu(op, torch.float32, M=M, N=N, T=12, B=1, H=2)
+    assert _last["f"].forward_func.sources[1].grid[0] > 1
+
+
+_last = {}
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("op", list(X.ZOO))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gpu(op, dtype):
-    M, N = (256, 1) if op in ("rwkv4", "hgrn") else (1, 1) if op == "mlstm_gates" else (64, 64)
-    ins, sts = X.zoo_case(op, 2, 40, 3, M, N, dtype)
+def test_gpu(op, dtype, M=None, N=None, T=40, B=2, H=3):
+    if M is None:
+        M, N = (256, 1) if op in ("rwkv4", "hgrn") else (1, 1) if op == "mlstm_gates" else (64, 64)
+    ins, sts = X.zoo_case(op, B, T, H, M, N, dtype)
     dev = "cuda:0"
     leaves = [x.to(dev).requires_grad_() for x in ins + sts]
     f = flex_rnn_b200.jit(X.ZOO[op])
+    _last["f"] = f
     outs = f(*leaves)
     g = torch.Generator().manual_seed(1)
     ups = [torch.randn(o.shape, generator=g) for o in outs]
